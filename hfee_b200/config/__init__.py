@@ -1,11 +1,12 @@
 from .llama import ConfigError, LlamaConfig, RopeScaling
 from .dobelix import DobelixConfig
 from .bamipel import BamipelConfig
+from .muvetar import MuvetarConfig
 from .spec import LayerSpec, ModelSpec, PartSpec, RunSpec, check_schedule
 from .registry import (Architecture, architecture, known_architectures, read_config_json,
                        register_architecture, resolve, resolve_model_dir)
 from .engine import EngineConfig
 
-__all__ = ["ConfigError", "BamipelConfig", "DobelixConfig", "LlamaConfig", "RopeScaling", "LayerSpec", "ModelSpec", "PartSpec",
+__all__ = ["ConfigError", "BamipelConfig", "DobelixConfig", "MuvetarConfig", "LlamaConfig", "RopeScaling", "LayerSpec", "ModelSpec", "PartSpec",
            "RunSpec", "check_schedule", "Architecture", "architecture", "known_architectures",
            "read_config_json", "register_architecture", "resolve", "resolve_model_dir", "EngineConfig"]

@@ -34,7 +34,7 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
                       const int* __restrict__ slot_of_token, T* __restrict__ out, int ld_o, int n, int heads,
                       float scale, int window, int chunk, const float* __restrict__ head_scale,
                       const float* __restrict__ head_bias, const T* __restrict__ gate, long long ld_gate,
-                      int gate_mode) {
+                      int gate_mode, const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, float out_scale) {
   pdl_wait();
   pdl_launch_dependents();
   __shared__ float q_s[WARPS][MAX_HD];
@@ -49,6 +49,7 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
   if (chunk > 0) lo = max(lo, (pos / chunk) * chunk);
   const float h_scale = (SIGMOID && head_scale != nullptr) ? head_scale[h] : 1.f;
   const float h_bias = (SIGMOID && head_bias != nullptr) ? head_bias[h] : 0.f;
+  const float r1 = dist_r1 != nullptr ? dist_r1[h] : 0.f, r2 = dist_r1 != nullptr ? dist_r2[h] : 0.f;
 
   const T* qrow = q + (long long)i * ld_q + (long long)h * hd;
   for (int d = lane; d < hd; d += 32) q_s[warp][d] = to_f32<T>(qrow[d]);
@@ -68,6 +69,7 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
       float acc = 0.f;
       for (int d = 0; d < hd; ++d) acc = fmaf(q_s[warp][d], to_f32<T>(kr[d]), acc);
       s = acc * scale;
+      if (dist_r1 != nullptr) s -= r1 * log1pf(r2 * (float)(pos - key));
     }
     float p;
     if constexpr (SIGMOID) {
@@ -93,7 +95,7 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
     }
   }
   T* orow = out + (long long)i * ld_o + (long long)h * vd;
-  float inv = SIGMOID ? 1.f : 1.f / l;
+  float inv = (SIGMOID ? 1.f : 1.f / l) * out_scale;
   const T* grow = gate_mode == GATE_ELEMENT ? gate + (long long)i * ld_gate + (long long)h * vd : nullptr;
   if (gate_mode == GATE_PER_HEAD) inv *= 1.f / (1.f + expf(-to_f32<T>(gate[(long long)i * ld_gate + h])));
 #pragma unroll
@@ -115,17 +117,17 @@ void launch_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool
                  int vd, const int* positions,
                  const int* slot_of_token, void* out, int ld_o, int n, int heads, float scale, int window, int chunk,
                  int sigmoid, const float* head_scale, const float* head_bias, const void* gate, long long ld_gate,
-                 int gate_mode, cudaStream_t stream) {
+                 int gate_mode, const float* dist_r1, const float* dist_r2, float out_scale, cudaStream_t stream) {
   long long tasks = (long long)n * heads;
   unsigned blocks = (unsigned)((tasks + WARPS - 1) / WARPS);
   if (sigmoid)
     hfee_launch(attention_simt_kernel<T, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const T*)q, ld_q, (const T*)k_pool,
                 (const T*)v_pool, c, vc, vd, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
-                head_bias, (const T*)gate, ld_gate, gate_mode);
+                head_bias, (const T*)gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale);
   else
     hfee_launch(attention_simt_kernel<T, false>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const T*)q, ld_q, (const T*)k_pool,
                 (const T*)v_pool, c, vc, vd, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
-                head_bias, (const T*)gate, ld_gate, gate_mode);
+                head_bias, (const T*)gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale);
 }
 }  // namespace
 
@@ -133,13 +135,17 @@ void launch_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool
 // value_dim: size of a value; v_pool is [pages][kv_heads][page_size][value_dim], or, with values_in_keys, the key
 // pool itself, whose leading value_dim dimensions are the values.  gate_mode: 0 none, 1 one number per output
 // element ([n, heads * value_dim]), 2 one number per head ([n, heads]); the output is multiplied by its sigmoid.
-HFEE_API int hfee_attention_simt_general(const void* q, int ld_q, const void* k_pool, const void* v_pool,
-                                         const int* block_table, int max_pages, int page_size, const int* positions,
-                                         const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
-                                         int head_dim, int value_dim, int values_in_keys, float scale, int window,
-                                         int chunk, int weights, const float* head_scale, const float* head_bias,
-                                         const void* gate, long long ld_gate, int gate_mode, int dtype,
-                                         cudaStream_t stream) {
+// dist_r1, dist_r2 (per head, or both null): r1[h] * ln(1 + r2[h] * (query position - key position)) is taken off the
+// score before the softmax.  out_scale multiplies the output.
+HFEE_API int hfee_attention_simt_distance(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                          const int* block_table, int max_pages, int page_size, const int* positions,
+                                          const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
+                                          int head_dim, int value_dim, int values_in_keys, float scale, int window,
+                                          int chunk, int weights, const float* head_scale, const float* head_bias,
+                                          const void* gate, long long ld_gate, int gate_mode, const float* dist_r1,
+                                          const float* dist_r2, float out_scale, int dtype, cudaStream_t stream) {
+  HFEE_REQUIRE((dist_r1 == nullptr) == (dist_r2 == nullptr), "attention_simt: the distance penalty needs both of its arrays");
+  HFEE_REQUIRE(dist_r1 == nullptr || weights == 0, "attention_simt: the distance penalty goes with the softmax");
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(head_dim > 0 && head_dim <= MAX_HD, "attention_simt: head_dim %d is outside 1..%d", head_dim, MAX_HD);
   HFEE_REQUIRE(value_dim > 0 && value_dim <= MAX_VD, "attention_simt: value_dim %d is outside 1..%d", value_dim, MAX_VD);
@@ -163,13 +169,27 @@ HFEE_API int hfee_attention_simt_general(const void* q, int ld_q, const void* k_
   }
   if (dtype == HFEE_F32)
     launch_simt<float>(q, ld_q, k_pool, v_pool, c, vc, value_dim, positions, slot_of_token, out, ld_o, n, heads, scale,
-                       window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, stream);
+                       window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale, stream);
   else if (dtype == HFEE_BF16)
     launch_simt<__nv_bfloat16>(q, ld_q, k_pool, v_pool, c, vc, value_dim, positions, slot_of_token, out, ld_o, n, heads,
-                               scale, window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, stream);
+                               scale, window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, dist_r1, dist_r2,
+                               out_scale, stream);
   else
     return hfee_fail(HFEE_ERR_ARG, "attention_simt: unknown dtype %d", dtype);
   return hfee_check_launch("attention_simt");
+}
+
+HFEE_API int hfee_attention_simt_general(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                         const int* block_table, int max_pages, int page_size, const int* positions,
+                                         const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
+                                         int head_dim, int value_dim, int values_in_keys, float scale, int window,
+                                         int chunk, int weights, const float* head_scale, const float* head_bias,
+                                         const void* gate, long long ld_gate, int gate_mode, int dtype,
+                                         cudaStream_t stream) {
+  return hfee_attention_simt_distance(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, positions, slot_of_token,
+                                      out, ld_o, n, heads, kv_heads, head_dim, value_dim, values_in_keys, scale, window,
+                                      chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, nullptr, nullptr,
+                                      1.f, dtype, stream);
 }
 
 HFEE_API int hfee_attention_simt_masked(const void* q, int ld_q, const void* k_pool, const void* v_pool,

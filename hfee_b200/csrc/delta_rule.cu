@@ -49,8 +49,8 @@ template <> __device__ __forceinline__ float silu_out<__nv_bfloat16>(float z) { 
 // MAXT: the most taps this instance takes (4 or CA_MAX_TAPS): the window and the weights live in registers
 template <typename T, int CH, int MAXT>
 __global__ void __launch_bounds__(CA_THREADS)
-conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict__ w, float* __restrict__ state,
-                const int* __restrict__ cu_tokens, const int* __restrict__ slots, T* __restrict__ out, long long ld_out,
+conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict__ w, const float* __restrict__ bias,
+                float* __restrict__ state, const int* __restrict__ cu_tokens, const int* __restrict__ slots, T* __restrict__ out, long long ld_out,
                 int width, int taps, int act, int mode) {
   const int req = blockIdx.y;
   const int c = (blockIdx.z * CA_THREADS + threadIdx.x) * CH;
@@ -65,7 +65,9 @@ conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict
   const int last = min(count, first + CA_TOKENS);
   float* st = state + (long long)slot * hist * width + c;                    // st[s * width]: input at index s - hist
   const T* xc = x + (long long)begin * ld_x + c;
-  float wv[CH][MAXT], win[MAXT][CH];
+  float wv[CH][MAXT], win[MAXT][CH], bv[CH];
+#pragma unroll
+  for (int k = 0; k < CH; ++k) bv[k] = bias != nullptr ? bias[c + k] : 0.f;
 #pragma unroll
   for (int j = 0; j < MAXT; ++j) {
 #pragma unroll
@@ -94,7 +96,7 @@ conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict
       float o[CH];
 #pragma unroll
       for (int k = 0; k < CH; ++k) {
-        float acc = 0.f;
+        float acc = bv[k];
 #pragma unroll
         for (int j = 0; j < MAXT; ++j) {
           const float in = (j == hist) ? xin[i][k] : win[j][k];
@@ -123,30 +125,30 @@ conv_act_kernel(const T* __restrict__ x, long long ld_x, const float* __restrict
 }
 
 template <typename T, int CH>
-int launch_conv_act_ch(const void* x, long long ld_x, const float* w, float* state, const int* cu_tokens, const int* slots,
+int launch_conv_act_ch(const void* x, long long ld_x, const float* w, const float* bias, float* state, const int* cu_tokens, const int* slots,
                        void* out, long long ld_out, int requests, int max_new, int width, int taps, int act, int write_state,
                        cudaStream_t stream) {
   const unsigned runs = (unsigned)((max_new + CA_TOKENS - 1) / CA_TOKENS);
   const unsigned cz = (unsigned)((width / CH + CA_THREADS - 1) / CA_THREADS);
   const bool together = write_state && runs == 1 && taps > 1;
   auto kernel = taps <= 4 ? conv_act_kernel<T, CH, 4> : conv_act_kernel<T, CH, CA_MAX_TAPS>;
-  hfee_launch(kernel, dim3(runs, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
+  hfee_launch(kernel, dim3(runs, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, bias, state, cu_tokens,
               slots, (T*)out, ld_out, width, taps, act, together ? (CA_OUT | CA_STATE) : CA_OUT);
   if (write_state && !together && taps > 1)
-    hfee_launch(kernel, dim3(1, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, state, cu_tokens,
+    hfee_launch(kernel, dim3(1, requests, cz), dim3(CA_THREADS), 0, stream, (const T*)x, ld_x, w, bias, state, cu_tokens,
                 slots, (T*)out, ld_out, width, taps, act, CA_STATE);
   return hfee_check_launch("conv_act");
 }
 
 template <typename T>
-int launch_conv_act(const void* x, long long ld_x, const float* w, float* state, const int* cu_tokens, const int* slots,
+int launch_conv_act(const void* x, long long ld_x, const float* w, const float* bias, float* state, const int* cu_tokens, const int* slots,
                     void* out, long long ld_out, int requests, int max_new, int width, int taps, int act, int write_state,
                     cudaStream_t stream) {
   const bool pairs = width % 2 == 0 && ld_x % 2 == 0 && ld_out % 2 == 0 && (uintptr_t)x % (2 * sizeof(T)) == 0 &&
                      (uintptr_t)out % (2 * sizeof(T)) == 0 && (uintptr_t)state % 8 == 0;
   if (pairs)
-    return launch_conv_act_ch<T, 2>(x, ld_x, w, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
-  return launch_conv_act_ch<T, 1>(x, ld_x, w, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
+    return launch_conv_act_ch<T, 2>(x, ld_x, w, bias, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
+  return launch_conv_act_ch<T, 1>(x, ld_x, w, bias, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -707,8 +709,8 @@ HFEE_API int hfee_conv_act_launches(int max_new, int taps, int write_state) {
   return (write_state && taps > 1 && max_new > CA_TOKENS) ? 2 : 1;
 }
 
-// act: 0 none, 1 SiLU.  state: [slots, taps - 1, width] float32.
-HFEE_API int hfee_conv_act(const void* x, long long ld_x, int dtype, const float* w, float* state, const int* cu_tokens,
+// act: 0 none, 1 SiLU.  state: [slots, taps - 1, width] float32.  bias: [width] added in front of the activation, or null.
+HFEE_API int hfee_conv_act(const void* x, long long ld_x, int dtype, const float* w, const float* bias, float* state, const int* cu_tokens,
                            const int* slots, void* out, long long ld_out, int requests, int max_new, int width, int taps,
                            int act, int write_state, cudaStream_t stream) {
   if (requests == 0 || max_new == 0) return HFEE_OK;
@@ -717,9 +719,9 @@ HFEE_API int hfee_conv_act(const void* x, long long ld_x, int dtype, const float
   HFEE_REQUIRE(ld_x >= width && ld_out >= width, "conv_act: a row stride is too small");
   HFEE_REQUIRE(act == ACT_NONE || act == ACT_SILU, "conv_act: unknown activation %d", act);
   if (dtype == HFEE_F32)
-    return launch_conv_act<float>(x, ld_x, w, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
+    return launch_conv_act<float>(x, ld_x, w, bias, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
   if (dtype == HFEE_BF16)
-    return launch_conv_act<__nv_bfloat16>(x, ld_x, w, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
+    return launch_conv_act<__nv_bfloat16>(x, ld_x, w, bias, state, cu_tokens, slots, out, ld_out, requests, max_new, width, taps, act, write_state, stream);
   return hfee_fail(HFEE_ERR_ARG, "conv_act: unknown dtype %d", dtype);
 }
 

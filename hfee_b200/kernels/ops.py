@@ -69,7 +69,21 @@ _SIGNATURES = {
     "hfee_latent_attention_mma": [_P, _L, _P, _P, _I, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _I, _P],
     "hfee_latent_attention_mma_supports": [_I, _I, _I],
     "hfee_head_linear": [_P, _L, _I, _I, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _I, _P],
-    "hfee_conv_act": [_P, _L, _I, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_conv_act": [_P, _L, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "hfee_attention_simt_distance": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _L, _I,
+                                     _P, _P, _F, _I, _P],
+    "hfee_add_sinusoid": [_P, _P, _I, _I, _F, _P],
+    "hfee_softcap": [_P, _L, _I, _I, _F, _P],
+    "hfee_clamped_glu": [_P, _L, _P, _L, _I, _I, _I, _F, _F, _I, _P],
+    "hfee_scaled_add_norm": [_P, _F, _P, _P, _F, _P, _L, _I, _I, _I, _P],
+    "hfee_depth_average": [_P, _P, _F, _P, _L, _P, _I, _I, _I, _P],
+    "hfee_mingru": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
+    "hfee_selective_scan": [_P, _L, _P, _L, _P, _L, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _F, _I, _I, _P],
+    "hfee_moe_route": [_P, _I, _I, _I, _F, _P, _P, _P],
+    "hfee_moe_plan": [_P, _I, _I, _P, _P, _P, _P, _I, _P],
+    "hfee_moe_gate_up": [_P, _L, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P, _L, _F, _F, _I, _I, _P],
+    "hfee_moe_down": [_P, _L, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P],
+    "hfee_moe_combine": [_P, _P, _I, _I, _P, _I, _I, _P],
     "hfee_conv_act_launches": [_I, _I, _I],
     "hfee_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P],
     "hfee_head_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
@@ -104,6 +118,8 @@ def library() -> ctypes.CDLL:
     lib.hfee_linear_attention_chunked_workspace.argtypes = [_I, _I, _I, _I, _I]
     lib.hfee_delta_rule_workspace.restype = _L
     lib.hfee_delta_rule_workspace.argtypes = [_I, _I, _I, _I, _I]
+    lib.hfee_moe_tile_rows.restype = _I
+    lib.hfee_moe_tile_rows.argtypes = []
     for name, sig in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
@@ -977,6 +993,34 @@ def attention_simt_general(q, k_pool, v_pool, block_table, page_size, positions,
                                            _rows(gate, "gate") if gate is not None else 0, int(gate_mode), _dt(q), _stream()), lib)
 
 
+def attention_simt_distance(q, k_pool, v_pool, block_table, page_size, positions, slot_of_token, out, heads, kv_heads,
+                            head_dim, value_dim, scale, r1, r2, out_scale=1.0, window=0) -> None:
+    """:func:`attention_simt_general` with a penalty on distance: ``r1[h] * ln(1 + r2[h] * (i - j))`` is taken off
+    the score of key j for query i of head h before the softmax (``r1``, ``r2`` float32 per head); the output is
+    multiplied by ``out_scale``."""
+    lib = library()
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token"); _i32(block_table, "block_table")
+    n = q.shape[0]
+    assert q.shape[1] == heads * head_dim and tuple(out.shape) == (n, heads * value_dim) and q.dtype == k_pool.dtype == out.dtype
+    assert k_pool.is_contiguous() and tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim)
+    assert v_pool.is_contiguous() and v_pool.dtype == q.dtype and tuple(v_pool.shape[1:]) == (kv_heads, page_size, value_dim)
+    for r in (r1, r2):
+        assert r.dtype == torch.float32 and r.is_contiguous() and r.numel() == heads
+    _check(lib.hfee_attention_simt_distance(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
+                                            block_table.shape[1], page_size, positions.data_ptr(), slot_of_token.data_ptr(),
+                                            out.data_ptr(), _rows(out, "attention out"), n, heads, kv_heads, head_dim,
+                                            value_dim, 0, float(scale), int(window or 0), 0, WEIGHTS_SOFTMAX, None, None, None, 0,
+                                            GATE_NONE, r1.data_ptr(), r2.data_ptr(), float(out_scale), _dt(q), _stream()), lib)
+
+
+def distance_attention(q, k_pool, v_pool, block_table, page_size, step, out, heads, kv_heads, head_dim, value_dim, scale, r1, r2,
+                       out_scale=1.0, window=0) -> None:
+    """Causal grouped-query softmax attention over the paged cache whose scores lose ``r1[h] * ln(1 + r2[h] * distance)``,
+    choosing the kernel for the dtype and the step."""
+    attention_simt_distance(q, k_pool, v_pool, block_table, page_size, step.positions, step.slot_of_token, out, heads, kv_heads,
+                            head_dim, value_dim, scale, r1, r2, out_scale, window)
+
+
 # The grouped-query kernels on the tensor cores take bfloat16 queries and keys and round the softmax weights to
 # bfloat16 for the product with the values; the CUDA-core kernel keeps scores and weights in float32.
 GATED_ATTENTION_ON_TENSOR_CORES = True
@@ -1105,8 +1149,8 @@ def head_linear(x: torch.Tensor, in_off: int, in_stride: int, w: torch.Tensor, o
 
 
 def conv_act(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor, activation: str = "silu",
-             write_state: bool = True) -> None:
-    """out[t, c] = act(sum_j weight[c, j] * x[t - taps + 1 + j, c]) per request of the step, inputs in front of the
+             write_state: bool = True, bias: Optional[torch.Tensor] = None) -> None:
+    """out[t, c] = act(bias[c] + sum_j weight[c, j] * x[t - taps + 1 + j, c]) per request of the step (``bias`` None: 0), inputs in front of the
     step's tokens taken from ``state`` [slots, taps - 1, width] (float32), which then takes the request's last
     taps - 1 inputs.  ``x`` and ``out`` are [n, width] views (any row stride) of the activations' dtype."""
     lib = library()
@@ -1115,7 +1159,8 @@ def conv_act(x: torch.Tensor, weight: torch.Tensor, state: torch.Tensor, step, o
     assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.shape[0] == width
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (taps - 1, width)
     assert out.shape == x.shape and out.dtype == x.dtype
-    _check(lib.hfee_conv_act(x.data_ptr(), _rows(x, "conv in"), _dt(x), weight.data_ptr(), state.data_ptr(),
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == width)
+    _check(lib.hfee_conv_act(x.data_ptr(), _rows(x, "conv in"), _dt(x), weight.data_ptr(), _ptr(bias), state.data_ptr(),
                              step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "conv out"), step.r,
                              step.max_new, width, taps, ACTIVATIONS[activation], int(write_state), _stream()), lib)
     if lib.hfee_conv_act_launches(step.max_new, taps, int(write_state)) > 1:
@@ -1248,6 +1293,169 @@ def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
     lib = library()
     assert x.dtype == torch.float32 and x.is_contiguous() and out.shape == x.shape
     _check(lib.hfee_cast_rows(x.data_ptr(), out.data_ptr(), _rows(out, "out"), x.shape[0], x.shape[1], _dt(out), _stream()), lib)
+
+
+# ---------------------------------------------------------------------------- scaled and averaged residual streams, capped logits
+def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, base: float = 10000.0) -> None:
+    """x[t, 2i] += sin(p_t * base^(-2i/width)), x[t, 2i+1] += cos of the same angle (float32 rows, float64 angles)."""
+    lib = library()
+    _i32(positions, "positions")
+    assert x.dtype == torch.float32 and x.is_contiguous() and positions.numel() == x.shape[0]
+    _check(lib.hfee_add_sinusoid(x.data_ptr(), positions.data_ptr(), x.shape[0], x.shape[1], float(base), _stream()), lib)
+
+
+def softcap_(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap) in place (float32 rows)."""
+    lib = library()
+    assert x.dtype == torch.float32 and x.dim() == 2
+    _check(lib.hfee_softcap(x.data_ptr(), _rows(x, "x"), x.shape[0], x.shape[1], float(cap), _stream()), lib)
+
+
+CLAMPED_SWISH_ALPHA = 1.702
+
+
+def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = CLAMPED_SWISH_ALPHA,
+                granule: Optional[int] = None) -> None:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); column layout
+    of :func:`swiglu`."""
+    lib = library()
+    n, inner = out.shape
+    assert gate_up.shape[1] == 2 * inner and gate_up.dtype == out.dtype
+    _check(lib.hfee_clamped_glu(gate_up.data_ptr(), _rows(gate_up, "gate_up"), out.data_ptr(), _rows(out, "out"), n, inner,
+                                int(granule or inner), float(limit), float(alpha), _dt(out), _stream()), lib)
+
+
+def scaled_add_norm(y: torch.Tensor, m: float, residual: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """residual += m * y (both float32), then out = residual / sqrt(mean(residual^2) + eps) * weight in ``out``'s dtype."""
+    lib = library()
+    n, width = residual.shape
+    assert y.dtype == residual.dtype == weight.dtype == torch.float32 and y.is_contiguous() and residual.is_contiguous()
+    assert y.shape == residual.shape and tuple(out.shape) == (n, width) and weight.numel() == width
+    _check(lib.hfee_scaled_add_norm(y.data_ptr(), float(m), residual.data_ptr(), weight.data_ptr(), float(eps), out.data_ptr(),
+                                    _rows(out, "out"), n, width, _dt(out), _stream()), lib)
+
+
+def scaled_add(y: torch.Tensor, m: float, residual: torch.Tensor) -> None:
+    """residual += m * y (both float32)."""
+    lib = library()
+    n, width = residual.shape
+    assert y.dtype == residual.dtype == torch.float32 and y.is_contiguous() and residual.is_contiguous() and y.shape == residual.shape
+    _check(lib.hfee_scaled_add_norm(y.data_ptr(), float(m), residual.data_ptr(), None, 0.0, None, 0, n, width, _DT[torch.float32],
+                                    _stream()), lib)
+
+
+def depth_average(residual: torch.Tensor, y: Optional[torch.Tensor], m: float, history: torch.Tensor, weights: torch.Tensor,
+                  index: int) -> None:
+    """r = residual + m * y (``y`` None: r = residual); history[index + 1, :n] = r;
+    residual = sum_(j <= index) weights[j] * history[j, :n] + weights[index + 1] * r.  ``history`` is
+    [entries, rows, width] float32 with entries >= index + 2."""
+    lib = library()
+    n, width = residual.shape
+    assert residual.dtype == history.dtype == weights.dtype == torch.float32 and residual.is_contiguous() and history.is_contiguous()
+    assert history.shape[0] >= index + 2 and history.shape[1] >= n and history.shape[2] == width and weights.numel() == index + 2
+    assert y is None or (y.dtype == torch.float32 and y.is_contiguous() and y.shape == residual.shape)
+    _check(lib.hfee_depth_average(residual.data_ptr(), _ptr(y), float(m), history.data_ptr(), history.stride(0), weights.data_ptr(),
+                                  int(index), n, width, _stream()), lib)
+
+
+# ---------------------------------------------------------------------------- elementwise recurrences
+def mingru(proj: torch.Tensor, z_off: int, x_off: int, g_off: int, z_bias: torch.Tensor, x_bias: torch.Tensor, state: torch.Tensor,
+           step, out: torch.Tensor, channels: int, write_state: bool = True) -> None:
+    """z = sigmoid(proj_z + z_bias), u = proj_x + x_bias, c = u + 1/2 where u >= 0 else sigmoid(u);
+    S_t = (1 - z) S_(t-1) + z c per channel from ``state`` [slots, channels] (float32, renewed);
+    out = S_t * silu(proj_g) in the activations' dtype."""
+    lib = library()
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == channels
+    assert out.dtype == proj.dtype and out.shape[1] == channels and max(z_off, x_off, g_off) + channels <= proj.shape[1]
+    _check(lib.hfee_mingru(proj.data_ptr(), _rows(proj, "proj"), z_off, x_off, g_off, z_bias.data_ptr(), x_bias.data_ptr(),
+                           state.data_ptr(), step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"),
+                           step.r, step.max_new, channels, int(write_state), _dt(proj), _stream()), lib)
+
+
+def selective_scan(x: torch.Tensor, dt_proj: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, z: torch.Tensor,
+                   a_log: torch.Tensor, d_skip: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor,
+                   out_scale: float = 1.0, write_state: bool = True) -> None:
+    """dt = softplus(dt_proj + dt_bias), A = -exp(a_log); S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n;
+    y_c = sum_n S[c, n] C_n + d_skip_c x_c; out = y * silu(z) * out_scale.  ``state`` [slots, channels, n] float32
+    is read and renewed; B and C are columns of ``bc``; ``dt_proj`` is float32."""
+    lib = library()
+    n, channels = x.shape
+    n_state = a_log.shape[1]
+    assert dt_proj.dtype == torch.float32 and tuple(dt_proj.shape) == (n, channels)
+    assert a_log.dtype == torch.float32 and a_log.is_contiguous() and a_log.shape[0] == channels
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (channels, n_state)
+    assert z.dtype == x.dtype == bc.dtype == out.dtype and z.shape == x.shape == out.shape
+    assert max(b_off, c_off) + n_state <= bc.shape[1]
+    _check(lib.hfee_selective_scan(x.data_ptr(), _rows(x, "x"), dt_proj.data_ptr(), _rows(dt_proj, "dt"), bc.data_ptr(), _rows(bc, "bc"),
+                                   b_off, c_off, z.data_ptr(), _rows(z, "z"), a_log.data_ptr(), d_skip.data_ptr(), dt_bias.data_ptr(),
+                                   state.data_ptr(), step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"),
+                                   step.r, step.max_new, channels, n_state, float(out_scale), int(write_state), _dt(x), _stream()), lib)
+
+
+# ---------------------------------------------------------------------------- routed experts
+def moe_tile_rows() -> int:
+    return int(library().hfee_moe_tile_rows())
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """Tiles a plan of ``pairs`` (token, choice) pairs over ``experts`` experts can need."""
+    return pairs // moe_tile_rows() + experts + 1
+
+
+def moe_route(logits: torch.Tensor, top: int, scale: float, choice: torch.Tensor, weight: torch.Tensor) -> None:
+    """Per row of ``logits`` [n, experts] (float32): softmax over all experts, the ``top`` largest (ties: the lower
+    expert) into ``choice`` [n, top] int32, their scores times ``scale`` into ``weight`` [n, top] float32."""
+    lib = library()
+    n, experts = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and weight.dtype == torch.float32
+    _i32(choice, "choice")
+    assert tuple(choice.shape) == (n, top) and tuple(weight.shape) == (n, top) and weight.is_contiguous()
+    _check(lib.hfee_moe_route(logits.data_ptr(), n, experts, top, float(scale), choice.data_ptr(), weight.data_ptr(), _stream()), lib)
+
+
+def moe_plan(choice: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor,
+             tile_row: torch.Tensor) -> None:
+    """Order the (token, choice) pairs by expert: ``offsets`` [experts + 1], ``order`` [pairs] (pair index at each
+    place), and the tiles of places (``tile_expert`` -1 = unused)."""
+    lib = library()
+    for t in (choice, offsets, order, tile_expert, tile_row):
+        _i32(t, "moe plan")
+    pairs = choice.numel()
+    assert offsets.numel() == experts + 1 and order.numel() >= pairs and tile_row.numel() == tile_expert.numel()
+    _check(lib.hfee_moe_plan(choice.data_ptr(), pairs, experts, offsets.data_ptr(), order.data_ptr(), tile_expert.data_ptr(),
+                             tile_row.data_ptr(), tile_expert.numel(), _stream()), lib)
+
+
+def moe_experts(x: torch.Tensor, top: int, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, limit: float,
+                offsets: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor, tile_row: torch.Tensor,
+                hidden: torch.Tensor, pair_out: torch.Tensor, alpha: float = CLAMPED_SWISH_ALPHA) -> None:
+    """For every (token, chosen expert e) pair: pair_out[pair] = W_down[e] act(W_gate[e] x, W_up[e] x) (float32), with the
+    clamped gated activation of :func:`clamped_glu`.  ``w_gate``, ``w_up``: [experts, inner, width]; ``w_down``:
+    [experts, width, inner]; ``hidden`` [pairs, inner] is scratch in the activations' dtype."""
+    lib = library()
+    n, width = x.shape
+    experts, inner = w_gate.shape[0], w_gate.shape[1]
+    pairs = n * top
+    tiles = min(tile_expert.numel(), moe_max_tiles(pairs, experts))
+    assert w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
+    assert tuple(w_up.shape) == (experts, inner, width) and tuple(w_down.shape) == (experts, width, inner)
+    assert x.dtype == w_gate.dtype == w_up.dtype == w_down.dtype == hidden.dtype
+    assert hidden.shape[0] >= pairs and hidden.shape[1] == inner
+    assert pair_out.dtype == torch.float32 and pair_out.is_contiguous() and pair_out.shape[0] >= pairs and pair_out.shape[1] == width
+    _check(lib.hfee_moe_gate_up(x.data_ptr(), _rows(x, "x"), top, w_gate.data_ptr(), w_up.data_ptr(), inner, width, offsets.data_ptr(),
+                                order.data_ptr(), tile_expert.data_ptr(), tile_row.data_ptr(), hidden.data_ptr(),
+                                _rows(hidden, "hidden"), float(limit), float(alpha), tiles, _dt(x), _stream()), lib)
+    _check(lib.hfee_moe_down(hidden.data_ptr(), _rows(hidden, "hidden"), top, w_down.data_ptr(), inner, width, offsets.data_ptr(),
+                             order.data_ptr(), tile_expert.data_ptr(), tile_row.data_ptr(), pair_out.data_ptr(), tiles, _dt(x),
+                             _stream()), lib)
+
+
+def moe_combine(pair_out: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, accumulate: bool) -> None:
+    """y[t] (+)= sum_k weight[t, k] * pair_out[t * top + k] (float32)."""
+    lib = library()
+    n, top = weight.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape[0] == n and pair_out.shape[1] == y.shape[1]
+    _check(lib.hfee_moe_combine(pair_out.data_ptr(), weight.data_ptr(), n, top, y.data_ptr(), y.shape[1], int(accumulate), _stream()), lib)
 
 
 def qk_norm_rope_cache(qk: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,

@@ -13,6 +13,9 @@ Categories and what each must provide:
                   (adds its output into ``residual``)
 ``feed_forward``  ``forward(xn[n,w], residual_f32[n,w], step)`` (adds into ``residual``)
 ``conv``          ``cache_need()`` (its history per request) and ``forward(x_f32[n,w], out[n,w], step, state)``
+``merge``         ``begin(residual_f32[n,w], step)`` in front of the layer's sublayers and ``forward(residual_f32[n,w],
+                  y_f32[n,w] or None, scale, step)`` after them: what the next layer reads, from this layer's result
+                  ``residual + scale * y`` and what earlier layers left
 ``block``         ``forward(residual_f32[n,w], step, cache, writes_cache)``, arranging the above; it is
                   built with ``parts={key: part}`` for the keys its layer spec names
 ``embedding``     ``forward(step, residual_f32[n,w])``
@@ -34,7 +37,7 @@ import torch
 from ..config.spec import PartSpec
 from ..weights.loader import TensorNeed
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "conv", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "conv", "merge", "block", "embedding", "head")
 _PARTS: Dict[Tuple[str, str], Type["Part"]] = {}
 
 

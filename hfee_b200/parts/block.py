@@ -137,6 +137,43 @@ class SandwichNormBlock(Block):
         self.ffn_out_norm.forward_add(y, residual)
 
 
+class ScaledPreNormBlock(Block):
+    """``y = x + m * mixer(norm(x)); r = y + m * feed_forward(norm(y))`` with one multiplier ``m`` on every
+    sublayer's output (spec ``residual_scale``), and an optional ``merge`` part that turns the layer's result r into
+    what the next layer reads.  ``ffn`` with ``ffn_norm`` is optional.  The scaled sum and the next norm leave in one
+    kernel; the last sum is the merge's, when there is one."""
+    needs = ("mixer", "mixer_norm")
+    graph_safe = True
+
+    def __init__(self, spec, tensors, rt, parts):
+        super().__init__(spec, tensors, rt, parts)
+        self.mixer, self.mixer_norm = parts["mixer"], parts["mixer_norm"]
+        self.feed_forward, self.ffn_norm = parts.get("ffn"), parts.get("ffn_norm")
+        if (self.feed_forward is None) != (self.ffn_norm is None):
+            raise ValueError("a feed-forward and its input norm come together")
+        self.merge = parts.get("merge")
+        self.width, self.scale = int(spec.width), float(spec.residual_scale)
+
+    def forward(self, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
+        rt, n = self.rt, step.n
+        xn = rt.scratch("block_normed", (rt.max_tokens, self.width))[:n]
+        y = rt.scratch("block_sublayer_out", (rt.max_tokens, self.width), torch.float32)[:n]
+        if self.merge is not None:
+            self.merge.begin(residual, step)
+        self.mixer_norm.forward(residual, xn)
+        OutputNormBlock._run(self.mixer, y, xn, step, cache, writes_cache)
+        if self.feed_forward is not None:
+            ops.tag("norm")
+            ops.scaled_add_norm(y, self.scale, residual, self.ffn_norm.weight, self.ffn_norm.eps, xn)
+            OutputNormBlock._run(self.feed_forward, y, xn, step)
+        if self.merge is not None:
+            self.merge.forward(residual, y, self.scale, step)
+        else:
+            ops.tag("norm")
+            ops.scaled_add(y, self.scale, residual)
+
+
+register_part("block", "scaled_pre_norm", ScaledPreNormBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "output_norm", OutputNormBlock)

@@ -13,7 +13,8 @@ from .base import Part, register_part
 
 class TokenEmbedding(Part):
     """``x[i,:] = table[token_i,:] * scale`` (hostfog/hfee internal/llm/forward.go:75-77 has no scale).
-    spec: ``vocab``, ``width``, ``scale`` (default 1)."""
+    spec: ``vocab``, ``width``, ``scale`` (default 1), ``sinusoid_base`` (default None; a base b adds the token's
+    position p as ``sin(p * b^(-2i/width))`` to entry 2i and the cosine of the same angle to entry 2i + 1)."""
     category = "embedding"
     graph_safe = True
 
@@ -25,17 +26,21 @@ class TokenEmbedding(Part):
         super().__init__(spec, tensors, rt)
         self.table = tensors["table"]
         self.scale = float(spec.get("scale", 1.0))
+        base = spec.get("sinusoid_base")
+        self.sinusoid_base = None if base is None else float(base)
 
     def forward(self, step: Any, residual: torch.Tensor) -> None:
         ops.tag("embed")
         ops.embed(self.table, step.token_ids, residual, step.slot_of_token, getattr(step, "feedback", None),
                   scale=self.scale)
+        if self.sinusoid_base is not None:
+            ops.add_sinusoid(residual, step.positions, self.sinusoid_base)
 
 
 class LinearHead(Part):
     """``logits = x . W^T * scale`` in float32 (internal/llm/forward.go:132-141).  spec: ``vocab``,
     ``width``, ``tied`` (use the embedding table as W, internal/llm/model.go:118-121), ``scale``
-    (default 1: no scaling pass)."""
+    (default 1: no scaling pass), ``softcap`` (default None; a cap c turns the logits into ``c * tanh(logits / c)``)."""
     category = "head"
     graph_safe = True
 
@@ -56,6 +61,8 @@ class LinearHead(Part):
         else:
             raise ValueError("the head has no weight and is not tied to the embedding")
         self.scale = float(spec.get("scale", 1.0))
+        cap = spec.get("softcap")
+        self.softcap = None if cap is None else float(cap)
 
     accepts_lazy_input = True        # the final norm may be fused into the product
 
@@ -68,6 +75,8 @@ class LinearHead(Part):
             ops.linear_normed(xn, self.weight, logits)
         if self.scale != 1.0:
             ops.scale_(logits, self.scale)
+        if self.softcap is not None:
+            ops.softcap_(logits, self.softcap)
 
 
 register_part("embedding", "token", TokenEmbedding)

@@ -1,0 +1,97 @@
+"""Routed mixture of small gated experts, with an optional expert that every token uses.
+
+    s = softmax(W_router h)  (float32, over all experts)         chosen = the ``top`` largest s
+    out = sum_(e in chosen) router_scale * s_e * expert_e(h)  +  shared(h)
+    expert(h) = W_down (g * sigmoid(alpha * g) * (u + 1)),  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
+
+The chosen weights are not renormalised.  The experts' tensors are stacked at load time (``[experts, inner, width]``
+twice and ``[experts, width, inner]``); the (token, choice) pairs are ordered by expert on the device, so the launches
+of a step depend on its token count alone and the step replays from a CUDA graph.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict
+
+import torch
+
+from ..config.spec import PartSpec
+from ..kernels import ops
+from ..weights.loader import TensorNeed
+from .base import Part, register_part
+from .gated_attention import pad8
+
+
+class RoutedExperts(Part):
+    """spec: ``width``, ``experts``, ``top``, ``router_scale``, ``inner``, ``limit``, ``alpha``, ``shared_inner`` and
+    ``shared_limit`` (both None: no shared expert).  ``forward(..., accumulate=False)`` stores the output."""
+    category = "feed_forward"
+    graph_safe = True
+    can_overwrite = True
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
+        w, f = spec.width, spec.inner
+        needs = {"router": TensorNeed((spec.experts, w))}
+        for e in range(spec.experts):
+            needs[f"e{e}.gate"] = TensorNeed((f, w))
+            needs[f"e{e}.up"] = TensorNeed((f, w))
+            needs[f"e{e}.down"] = TensorNeed((w, f))
+        if spec.get("shared_inner") is not None:
+            s = spec.shared_inner
+            needs.update({"shared.gate": TensorNeed((s, w)), "shared.up": TensorNeed((s, w)), "shared.down": TensorNeed((w, s))})
+        return needs
+
+    def __init__(self, spec, tensors, rt):
+        super().__init__(spec, tensors, rt)
+        self.width, self.experts, self.top = int(spec.width), int(spec.experts), int(spec.top)
+        self.inner, self.limit, self.alpha = int(spec.inner), float(spec.limit), float(spec.alpha)
+        self.router_scale = float(spec.router_scale)
+        if not 1 <= self.top <= self.experts:
+            raise ValueError(f"top {self.top} is outside 1..{self.experts}")
+        self.w_router = tensors["router"]
+        self.w_gate = torch.stack([tensors[f"e{e}.gate"] for e in range(self.experts)]).contiguous()
+        self.w_up = torch.stack([tensors[f"e{e}.up"] for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+        self.shared_inner = spec.get("shared_inner")
+        if self.shared_inner is not None:
+            self.shared_inner, self.shared_limit = int(self.shared_inner), float(spec.shared_limit)
+            self.w_shared_in = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0).contiguous()
+            self.w_shared_down = tensors["shared.down"]
+        pairs = rt.max_tokens * self.top
+        self.tiles = ops.moe_max_tiles(pairs, self.experts)
+
+    def forward(self, xn, out: torch.Tensor, step: Any, accumulate: bool = True) -> None:
+        n, rt, top = step.n, self.rt, self.top
+        xn = xn if isinstance(xn, torch.Tensor) else xn.tensor()
+        i32 = torch.int32
+        logits = rt.scratch("moe_logits", (rt.max_tokens, self.experts), torch.float32)[:n]
+        choice = rt.scratch("moe_choice", (rt.max_tokens, top), i32)[:n]
+        weight = rt.scratch("moe_weight", (rt.max_tokens, top), torch.float32)[:n]
+        offsets = rt.scratch("moe_offsets", (self.experts + 1,), i32)
+        order = rt.scratch("moe_order", (rt.max_tokens * top,), i32)
+        tile_expert = rt.scratch("moe_tile_expert", (self.tiles,), i32)
+        tile_row = rt.scratch("moe_tile_row", (self.tiles,), i32)
+        hidden = rt.scratch("moe_hidden", (rt.max_tokens * top, pad8(self.inner)))[:n * top, :self.inner]
+        pair_out = rt.scratch("moe_pair_out", (rt.max_tokens * top, self.width), torch.float32)[:n * top]
+        ops.tag("router")
+        ops.linear(xn, self.w_router, logits)
+        ops.moe_route(logits, top, self.router_scale, choice, weight)
+        ops.moe_plan(choice, self.experts, offsets, order, tile_expert, tile_row)
+        ops.tag("experts")
+        ops.moe_experts(xn, top, self.w_gate, self.w_up, self.w_down, self.limit, offsets, order, tile_expert, tile_row,
+                        hidden, pair_out, self.alpha)
+        if self.shared_inner is not None:
+            s = self.shared_inner
+            gu = rt.scratch("ffn_gate_up", (rt.max_tokens, pad8(2 * s)))[:n, :2 * s]
+            h = rt.scratch("ffn_hidden", (rt.max_tokens, pad8(s)))[:n, :s]
+            ops.tag("gate_up")
+            ops.linear(xn, self.w_shared_in, gu)
+            ops.clamped_glu(gu, h, self.shared_limit, self.alpha)
+            ops.tag("down")
+            ops.linear(h, self.w_shared_down, out, accumulate=accumulate)
+            accumulate = True
+        ops.tag("experts")
+        ops.moe_combine(pair_out, weight, out, accumulate)
+
+
+register_part("feed_forward", "routed_experts", RoutedExperts)

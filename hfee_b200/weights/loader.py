@@ -51,7 +51,8 @@ class TensorNeed:
     ``role`` decides the dtype it is kept in and how random weights draw it:
     ``matrix``/``table`` (GEMM operands and embedding tables: the compute dtype,
     N(0, 0.02)), ``scale`` (norm weights: float32, 1 + N(0, 0.02)), ``vector``
-    (float32, N(0, 0.02)), ``index`` (integer tables: int32, zeros)."""
+    (float32, N(0, 0.02)), ``positive`` (float32, |N(0, 0.02)|), ``average`` (float32, the weights of a mean:
+    1/count + N(0, 0.02)), ``index`` (integer tables: int32, zeros)."""
     shape: Tuple[int, ...]
     role: str = "matrix"
     optional: bool = False

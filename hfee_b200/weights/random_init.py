@@ -3,7 +3,8 @@ configuration and a seed.
 
 Every tensor is drawn from a generator seeded by (seed, tensor name), so its values
 do not depend on the order or the set of tensors written.  Matrices and tables are
-N(0, 0.02), norm scales 1 + N(0, 0.02), integer tables zeros.  The reference has no
+N(0, 0.02), norm scales 1 + N(0, 0.02), integer tables zeros, ``positive`` vectors |N(0, 0.02)|, ``average``
+weights 1/count + N(0, 0.02).  The reference has no
 such mode (it only reads GGUF files, hostfog/hfee internal/llm/model.go:58-71).
 """
 from __future__ import annotations
@@ -36,6 +37,10 @@ def random_tensors(needs: Mapping[str, TensorNeed], seed: int, dtype: torch.dtyp
         t = torch.randn(need.shape, generator=g, dtype=torch.float32) * std
         if need.role == "scale":
             t += 1.0
+        elif need.role == "positive":
+            t = t.abs()
+        elif need.role == "average":
+            t += 1.0 / max(1, t.numel())
         out[name] = t.to(dtype)
     return out
 
