@@ -20,7 +20,9 @@ layers, named beside the full number in ``config``), ``--dtype float32`` the tru
 attention with decay, chunked sigmoid attention, short convolutions, norms on the sublayers' outputs) beside a
 Llama model of the same width, heads, feed-forward and number of layers, with what each class of kernels costs;
 ``--design bamipel`` the same for a Bamipel model (gated delta rule, latent attention under a sliding window, gated
-grouped-query attention, norms on both sides of every sublayer, a relu^2 feed-forward).
+grouped-query attention, norms on both sides of every sublayer, a relu^2 feed-forward); ``--design muvetar`` for a
+Muvetar model (minGRU layers in turn with softmax attention under a logarithmic distance penalty beside a selective
+scan; routed experts with a shared one whose active sizes add up to the dense feed-forward; depth averaging).
 ``--breakdown`` prints, instead of the line above, what each class of kernels costs inside the decode
 step at batch 1, 8 and 64 and inside the prompt pass: the step is timed again with that class's
 launches left out (results wrong, timing not), and the difference is the class's cost in place.
@@ -197,7 +199,30 @@ def bamipel_like(model, layers, window=512):
     return {"architecture": "Bamipel", "vocab": model["vocab_size"], "width": width, "layers": out, "norm": {"eps": 1e-5}}
 
 
-DESIGNS = {"dobelix": dobelix_like, "bamipel": bamipel_like}
+def muvetar_like(model, layers, experts=16, top=2):
+    """A Muvetar configuration of the layer sizes of the Llama configuration ``model``: in turn a parallel mixer
+    (distance attention with the Llama heads beside a selective scan of the model's width, 16 state entries per channel, a
+    step-size rank of a sixteenth of the width, four taps) and a minGRU of the model's width; every layer with ``experts``
+    routed experts of a quarter of the dense feed-forward each (``top`` chosen) and a shared one of half of it, so that a
+    token passes as many feed-forward weights as in the dense model."""
+    h, kv, hd = model["num_attention_heads"], model["num_key_value_heads"], model["head_dim"]
+    width, ff = model["hidden_size"], model["intermediate_size"]
+    mlp = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 1.0},
+           "expert": {"ff": ff // 4, "limit": 7.0}, "shared": {"ff": ff // 2, "limit": 7.0}}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            out.append({"type": "parallel", "mlp": mlp,
+                        "mixer": {"left": {"heads": h, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5},
+                                  "right": {"inner": width, "state": 16, "dt_rank": width // 16, "conv": 4},
+                                  "left_scale": 1.0, "right_scale": 1.0}})
+        else:
+            out.append({"type": "mingru", "mlp": mlp, "mixer": {"width": width}})
+    return {"architecture": "Muvetar", "vocab": model["vocab_size"], "width": width, "layers": out, "norm": {"eps": 1e-5},
+            "residual_mult": 1.0, "logit_softcap": 30.0}
+
+
+DESIGNS = {"dobelix": dobelix_like, "bamipel": bamipel_like, "muvetar": muvetar_like}
 # kernel classes (the names the parts tag their launches with) that only some layers of a design have: class -> the layer
 # types that have it; every other class is counted once per layer ("head": once per model)
 DESIGN_CLASSES = {
@@ -205,9 +230,11 @@ DESIGN_CLASSES = {
                 "rope": ("attention",), "attention": ("attention",)},
     "bamipel": {"conv": ("delta",), "delta_rule": ("delta",), "gate": ("delta",), "rope": ("attention", "latent_attention"),
                 "attention": ("attention", "latent_attention"), "fold": ("latent_attention",), "expand": ("latent_attention",)},
+    "muvetar": {"conv": ("parallel",), "scan_proj": ("parallel",), "scan": ("parallel", "mingru"), "rope": ("parallel",),
+                "attention": ("parallel",), "router": ("parallel", "mingru"), "experts": ("parallel", "mingru")},
 }
-CLASS_ORDER = ("conv", "norm", "qkv", "rope", "fold", "attention", "expand", "linear_attention", "delta_rule", "gate", "o",
-               "gate_up", "up", "down", "head")
+CLASS_ORDER = ("conv", "norm", "qkv", "rope", "fold", "attention", "expand", "linear_attention", "delta_rule", "scan_proj", "scan",
+               "gate", "o", "router", "experts", "gate_up", "up", "down", "head")
 
 
 def design_comparison(args):
@@ -281,12 +308,12 @@ def design_comparison(args):
 
         if name == "llama":
             having = {"rope": layers, "attention": layers, "gate_up": layers, "up": 0}
-            having.update({c: 0 for c in ("conv", "gate", "linear_attention", "delta_rule", "fold", "expand")})
+            having.update({c: 0 for cs in DESIGN_CLASSES.values() for c in cs if c not in having})
         else:
             kinds = [l["type"] for l in cfg["layers"]]
             having = {c: sum(kinds.count(k) for k in types) for c, types in DESIGN_CLASSES[name].items()}
             having.update({c: 0 for cs in DESIGN_CLASSES.values() for c in cs if c not in having})
-            having.update({"gate_up": layers, "up": 0} if name == "dobelix" else {"gate_up": 0, "up": layers})
+            having.update({"gate_up": 0, "up": layers} if name == "bamipel" else {"gate_up": layers, "up": 0})
 
         def classes_of(measure, rounds=3):
             res = {}

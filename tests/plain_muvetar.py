@@ -167,10 +167,16 @@ def clamped_expert(h, W, p, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ W[p + "down"].T
 
 
+ROUTE_MARGINS = []       # per call of route(): the smallest gap between the last chosen logit and the best one left out
+
+
 def route(h, W_router, top, scale):
     """(chosen experts [T, top], their weights [T, top]): softmax over all experts, the ``top`` largest,
     times ``scale``, not renormalised."""
     z = h @ W_router.T
+    if top < z.shape[1]:
+        ranked = -np.sort(-z, axis=1)
+        ROUTE_MARGINS.append(float(np.min(ranked[:, top - 1] - ranked[:, top])))
     z = z - z.max(axis=1, keepdims=True)
     s = np.exp(z)
     s /= s.sum(axis=1, keepdims=True)
@@ -218,3 +224,11 @@ def forward(cfg, W, tokens, return_layers=False):
     logits = rms_norm(x, W["final.norm"], eps) @ W["head"].T
     logits = cap * np.tanh(logits / cap)
     return (logits, np.stack(streams)) if return_layers else logits
+
+
+def greedy(cfg, W, prompt, n):
+    """``n`` tokens after ``prompt``, each the argmax of the last position's logits (ties: the lowest id)."""
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(np.argmax(forward(cfg, W, tokens)[-1])))
+    return tokens[len(prompt):]
