@@ -54,8 +54,9 @@ def clear_routes(tensors, cfg, loud=6.0):
     """Make every router's choice a clear call, so that rounding cannot flip one.  Every layer with experts gets
     embedding dimensions of its own, one per expert, which its router reads with weight 1 (and everything else with
     a tenth of its random weight); token t is loud in the dimensions of the ``top`` experts from t % experts on
-    (cyclically).  Which experts are chosen is then settled; positions, mixers and earlier layers still move the
-    scores, so the chosen experts' weights differ from token to token."""
+    (cyclically), and no sublayer's output projection writes into those dimensions.  Which experts are chosen is then
+    settled; positions, mixers and earlier layers still move the scores, so the chosen experts' weights differ from
+    token to token."""
     emb = tensors["embed"]
     at = ROUTE_AT
     for i, layer in enumerate(cfg["layers"]):
@@ -74,6 +75,9 @@ def clear_routes(tensors, cfg, loud=6.0):
             for k in range(top):
                 emb[t, at + (t + k) % experts] = loud
         at += experts
+    for name, t in tensors.items():          # no sublayer writes into the marks: they reach every router as the embedding left them
+        if name.endswith((".o", ".down")):
+            t[ROUTE_AT:at] = 0.0
 
 
 def write_model(path, cfg, seed, dtype="bfloat16", edit=None, routes=True):
