@@ -43,6 +43,13 @@ struct AttnParams {
   const float2* rope_cs;       // [token][rope_dim/2] (cos, sin); null: no rotation
   int rope_dim, rope_interleaved;
   __nv_bfloat16* k_write; __nv_bfloat16* v_write;      // the pools, writable; null: this run only reads the cache
+  // Kernels with DIST: keys of cache.head_dim and values of vcache.head_dim elements (multiples of 8, at most HD;
+  // the tiles are zero-filled up to HD), r1[h] * log2(1 + r2[h] * (query position - key position)) taken off the
+  // score in log2 units (ln(x) * log2(e) = log2(x): r1 is used as it is),
+  // and the output times out_scale.
+  PagedCache vcache;
+  const float* dist_r1; const float* dist_r2;
+  float out_scale;
 };
 
 // Rotates the 16-byte piece of a head that starts at dim `a` (a multiple of 8): pairs (i, i + half)
@@ -128,7 +135,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // state of its own, and the warps' results are merged at the end (decode: few rows, many keys).
 // STAGES key/value blocks are in flight per CTA (cp.async groups): decode CTAs, which do little
 // arithmetic per block, keep more of them in flight than prefill CTAs.
-template <int HD, int NWARPS, bool KSPLIT, int STAGES>
+template <int HD, int NWARPS, bool KSPLIT, int STAGES, bool DIST>
 __global__ void __launch_bounds__(NWARPS * 32)
 attention_mma_kernel(AttnParams p) {
   static_assert(!KSPLIT || NWARPS * 16 == BLOCK_N, "key-split mode needs 16 keys per warp");
@@ -152,6 +159,8 @@ attention_mma_kernel(AttnParams p) {
   const int tile = (int)(gridDim.y / p.num_splits) - 1 - (int)(blockIdx.y / p.num_splits);
   const int split = blockIdx.y % p.num_splits;
   const int kvh = blockIdx.x, r = blockIdx.z;
+  const int kdim = DIST ? p.cache.head_dim : HD, vdim = DIST ? p.vcache.head_dim : HD;   // real key and value sizes
+  const float c_log2 = DIST ? 1.f : p.scale_log2;        // DIST turns the scores into log2 units itself
 
   const int tok0 = p.cu_tokens[r], n_new = p.cu_tokens[r + 1] - tok0;
   const int t_first = tile * p.tokens_per_tile;
@@ -201,15 +210,18 @@ attention_mma_kernel(AttnParams p) {
       // a block lies inside one page (both are powers of two, blocks start at multiples of 64): one lookup
       const int pos0 = block * BLOCK_N;
       const int page = p.cache.block_table[(long long)slot * p.cache.max_pages + (pos0 >> p.cache.page_shift)];
-      const long long base = (long long)page * p.cache.page_stride +
-                             ((long long)kvh * p.cache.page_size + (pos0 & (p.cache.page_size - 1))) * HD;
+      // offsets count rows of HD elements; with DIST they count rows (the pools' row sizes differ)
+      const long long base = DIST ? (long long)page * (p.cache.kv_heads * p.cache.page_size) +
+                                        (long long)kvh * p.cache.page_size + (pos0 & (p.cache.page_size - 1))
+                                  : (long long)page * p.cache.page_stride +
+                                        ((long long)kvh * p.cache.page_size + (pos0 & (p.cache.page_size - 1))) * HD;
 #pragma unroll
       for (int i = 0; i < PIECES; ++i) {
         const int idx = tid + i * THREADS;
         const int row = idx / CHUNKS, ch = idx % CHUNKS;
         const int pos = pos0 + row;
         ok[i] = idx < BLOCK_N * CHUNKS && pos >= key_lo && pos <= pos_last;
-        off[i] = ok[i] ? base + (long long)row * HD + ch * 8 : 0;
+        off[i] = ok[i] ? (DIST ? base + row : base + (long long)row * HD + ch * 8) : 0;
       }
     } else {
 #pragma unroll
@@ -218,7 +230,8 @@ attention_mma_kernel(AttnParams p) {
         const int row = idx / CHUNKS, ch = idx % CHUNKS;
         const int pos = block * BLOCK_N + row;
         ok[i] = idx < BLOCK_N * CHUNKS && pos >= key_lo && pos <= pos_last;
-        off[i] = ok[i] ? paged_offset(p.cache, slot, pos, kvh) + ch * 8 : 0;
+        off[i] = ok[i] ? (DIST ? paged_offset(p.cache, slot, pos, kvh) / p.cache.head_dim
+                               : paged_offset(p.cache, slot, pos, kvh) + ch * 8) : 0;
       }
     }
 #pragma unroll
@@ -226,8 +239,14 @@ attention_mma_kernel(AttnParams p) {
       const int idx = tid + i * THREADS;
       if (idx < BLOCK_N * CHUNKS) {
         const int row = idx / CHUNKS, ch = idx % CHUNKS;
-        cp_async16(kd + row * PITCH + ch * 8, p.k_pool + off[i], ok[i]);
-        cp_async16(vd + row * PITCH + ch * 8, p.v_pool + off[i], ok[i]);
+        if constexpr (DIST) {
+          const bool in_k = ok[i] && ch * 8 < kdim, in_v = ok[i] && ch * 8 < vdim;
+          cp_async16(kd + row * PITCH + ch * 8, p.k_pool + (in_k ? off[i] * kdim + ch * 8 : 0), in_k);
+          cp_async16(vd + row * PITCH + ch * 8, p.v_pool + (in_v ? off[i] * vdim + ch * 8 : 0), in_v);
+        } else {
+          cp_async16(kd + row * PITCH + ch * 8, p.k_pool + off[i], ok[i]);
+          cp_async16(vd + row * PITCH + ch * 8, p.v_pool + off[i], ok[i]);
+        }
       }
     }
   };
@@ -245,6 +264,17 @@ attention_mma_kernel(AttnParams p) {
   for (int h = 0; h < 2; ++h) {
     int row = wrow + g + 8 * h;
     row_pos[h] = row < rows_used ? pos_first + row / p.group : -1;      // -1: every key masked
+  }
+  float row_r1[2] = {0.f, 0.f}, row_r2[2] = {0.f, 0.f};
+  if constexpr (DIST) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = wrow + g + 8 * h;
+      if (row < rows_used) {
+        row_r1[h] = p.dist_r1[kvh * p.group + row % p.group];
+        row_r2[h] = p.dist_r2[kvh * p.group + row % p.group];
+      }
+    }
   }
 
   // one cp.async group per block, committed even when empty, so that "all but the newest
@@ -278,7 +308,8 @@ attention_mma_kernel(AttnParams p) {
         const float2* tab = p.rope_cs ? p.rope_cs + (long long)(tok0 + t) * rope_half : nullptr;
         pieces = rope_piece(head, tab, ch * 8, p.rope_dim, p.rope_interleaved, v, v2);
       } else {
-        v = *reinterpret_cast<const uint4*>(p.q + (long long)(tok0 + t) * p.ld_q + (long long)(kvh * p.group + hg) * HD + ch * 8);
+        if (ch * 8 < kdim)
+          v = *reinterpret_cast<const uint4*>(p.q + (long long)(tok0 + t) * p.ld_q + (long long)(kvh * p.group + hg) * kdim + ch * 8);
       }
     }
     if (pieces >= 1) *reinterpret_cast<uint4*>(q_s + row * PITCH + ch * 8) = v;
@@ -354,8 +385,17 @@ attention_mma_kernel(AttnParams p) {
 
     // ---- mask (only in blocks that reach past a row's position or below its window), online
     // softmax on the raw scores: p = 2^(s*c - m*c) with c = scale*log2(e) folded into one FMA
-    const float c_log2 = p.scale_log2;
     const int key0 = b * BLOCK_N + wkey;                       // first key this warp visits in the block
+    if constexpr (DIST) {
+#pragma unroll
+      for (int nt = 0; nt < WKEYS / 8; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int h = j >> 1;
+          const float dist = (float)max(row_pos[h] - (key0 + nt * 8 + 2 * c + (j & 1)), 0);
+          s[nt][j] = fmaf(s[nt][j], p.scale_log2, -row_r1[h] * __log2f(fmaf(row_r2[h], dist, 1.f)));
+        }
+    }
     const int row_lo = min(row_pos_min, row_pos_max), row_hi = row_pos_max;
     const bool need_mask = key0 + WKEYS - 1 > row_lo || (p.window > 0 && key0 <= row_hi - p.window);
     float m_new[2] = {m_run[0], m_run[1]};
@@ -445,7 +485,7 @@ attention_mma_kernel(AttnParams p) {
       for (int i = 0; i < HD / 8; ++i)
         *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
       // running maxima are in raw score units; merges and partial results use log2 units
-      if (c == 0) { mm[warp * 16 + row] = m_run[h] * p.scale_log2; ml[warp * 16 + row] = l_run[h]; }
+      if (c == 0) { mm[warp * 16 + row] = m_run[h] * c_log2; ml[warp * 16 + row] = l_run[h]; }
     }
     __syncthreads();
     for (int idx = tid; idx < rows_used * (HD / 2); idx += THREADS) {
@@ -465,8 +505,9 @@ attention_mma_kernel(AttnParams p) {
       int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
       if (p.num_splits == 1) {
         float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * HD;
-        *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+        if constexpr (DIST) inv *= p.out_scale;
+        __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * vdim;
+        if (d < vdim) *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
       } else {
         long long pi = ((long long)(tok0 + t) * p.heads + head) * p.num_splits + split;
         *reinterpret_cast<float2*>(p.part_o + pi * HD + d) = make_float2(o0, o1);
@@ -481,11 +522,12 @@ attention_mma_kernel(AttnParams p) {
     int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
     if (p.num_splits == 1) {
       float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
-      __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * HD;
+      if constexpr (DIST) inv *= p.out_scale;
+      __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * vdim;
 #pragma unroll
       for (int i = 0; i < HD / 8; ++i) {
         __nv_bfloat162 v = __floats2bfloat162_rn(o_acc[i][2 * h] * inv, o_acc[i][2 * h + 1] * inv);
-        *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * c) = v;
+        if (!DIST || i * 8 < vdim) *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * c) = v;
       }
     } else {
       long long idx = ((long long)(tok0 + t) * p.heads + head) * p.num_splits + split;
@@ -494,7 +536,7 @@ attention_mma_kernel(AttnParams p) {
       for (int i = 0; i < HD / 8; ++i)
         *reinterpret_cast<float2*>(dst + i * 8 + 2 * c) = make_float2(o_acc[i][2 * h], o_acc[i][2 * h + 1]);
       if (c == 0) {
-        p.part_ml[idx * 2] = m_run[h] * p.scale_log2;
+        p.part_ml[idx * 2] = m_run[h] * c_log2;
         p.part_ml[idx * 2 + 1] = l_run[h];
       }
     }
@@ -509,7 +551,8 @@ attention_mma_kernel(AttnParams p) {
 constexpr int COMBINE_WARPS = 4;
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                         __nv_bfloat16* __restrict__ out, int ld_o, int heads, int hd, int num_splits, int pairs) {
+                         __nv_bfloat16* __restrict__ out, int ld_o, int heads, int hd, int num_splits, int pairs,
+                         int stride, float out_scale) {      // stride: floats per partial output (>= hd, a multiple of 4)
   pdl_wait();
   pdl_launch_dependents();
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -531,14 +574,14 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
       float4 v[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        v[i] = (s0 + i < num_splits && d < hd) ? *reinterpret_cast<const float4*>(part_o + (base + s0 + i) * hd + d)
+        v[i] = (s0 + i < num_splits && d < hd) ? *reinterpret_cast<const float4*>(part_o + (base + s0 + i) * stride + d)
                                                : make_float4(0.f, 0.f, 0.f, 0.f);
       if (!have_w) {
         float m = warp_max(ml.x);
         w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m);
         float l = 0.f;
         for (int s = 0; s < num_splits; ++s) l += __shfl_sync(0xffffffffu, w * ml.y, s);     // split order
-        inv = l > 0.f ? 1.f / l : 0.f;
+        inv = l > 0.f ? out_scale / l : 0.f;
         have_w = true;
       }
 #pragma unroll
@@ -557,7 +600,7 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
   }
 }
 
-template <int HD, bool KSPLIT, int STAGES>
+template <int HD, bool KSPLIT, int STAGES, bool DIST>
 int launch(const AttnParams& p, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
   constexpr int NWARPS = 4;
   constexpr int PITCH = HD + 8;
@@ -565,25 +608,25 @@ int launch(const AttnParams& p, int q_tiles, int kv_heads, int requests, cudaStr
   size_t smem = (size_t)(ROWS + 2 * STAGES * BLOCK_N) * PITCH * sizeof(__nv_bfloat16);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NWARPS, KSPLIT, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NWARPS, KSPLIT, STAGES, DIST>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return hfee_fail(HFEE_ERR_CUDA, "attention_mma: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   dim3 grid((unsigned)kv_heads, (unsigned)(q_tiles * p.num_splits), (unsigned)requests);
-  hfee_launch(attention_mma_kernel<HD, NWARPS, KSPLIT, STAGES>, dim3(grid), dim3(NWARPS * 32), smem, stream, p);
+  hfee_launch(attention_mma_kernel<HD, NWARPS, KSPLIT, STAGES, DIST>, dim3(grid), dim3(NWARPS * 32), smem, stream, p);
   return hfee_check_launch("attention_mma");
 }
 
-template <int HD>
+template <int HD, bool DIST = false>
 int dispatch_mode(const AttnParams& p, bool ksplit, int q_tiles, int kv_heads, int requests, cudaStream_t stream) {
-  if (!ksplit) return launch<HD, false, 2>(p, q_tiles, kv_heads, requests, stream);
+  if (!ksplit) return launch<HD, false, 2, DIST>(p, q_tiles, kv_heads, requests, stream);
   // decode: keep four key blocks in flight per CTA when the grid is small enough that the larger
   // shared-memory footprint (fewer CTAs per SM) does not add a wave; otherwise two
   constexpr int DEEP = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
   long long ctas = (long long)p.num_splits * kv_heads * requests;
-  if (DEEP > 2 && ctas <= 3 * hfee_sm_count()) return launch<HD, true, DEEP>(p, q_tiles, kv_heads, requests, stream);
-  return launch<HD, true, 2>(p, q_tiles, kv_heads, requests, stream);
+  if (DEEP > 2 && ctas <= 3 * hfee_sm_count()) return launch<HD, true, DEEP, DIST>(p, q_tiles, kv_heads, requests, stream);
+  return launch<HD, true, 2, DIST>(p, q_tiles, kv_heads, requests, stream);
 }
 
 }  // namespace
@@ -599,12 +642,17 @@ namespace {
 struct RopeFusion {
   const void* qkv; int ld_qkv; const float* cs; int rope_dim; int interleaved; void* k_write; void* v_write;
 };
+// A penalty on distance and sizes of their own for keys and values (head_dim of the call is then the tile size)
+struct DistanceOption {
+  int key_dim, value_dim; const float* r1; const float* r2; float out_scale;
+};
 
 int attention_mma_impl(const void* q, int ld_q, const void* k_pool, const void* v_pool,
                        const int* block_table, int max_pages, int page_size, const int* cu_tokens,
                        const int* slots, const int* context_before, void* out, int ld_o, int n_tokens,
                        int requests, int max_new, int heads, int kv_heads, int head_dim, float scale,
-                       int window, int num_splits, float* scratch, const RopeFusion* rope, cudaStream_t stream) {
+                       int window, int num_splits, float* scratch, const RopeFusion* rope, cudaStream_t stream,
+                       const DistanceOption* dist = nullptr) {
   if (n_tokens == 0 || requests == 0) return HFEE_OK;
   HFEE_REQUIRE(head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 256,
                "attention_mma: head_dim %d must be a multiple of 16 in 16..256", head_dim);
@@ -629,8 +677,10 @@ int attention_mma_impl(const void* q, int ld_q, const void* k_pool, const void* 
   p.q = (const __nv_bfloat16*)q; p.ld_q = ld_q;
   p.out = (__nv_bfloat16*)out; p.ld_o = ld_o;
   p.k_pool = (const __nv_bfloat16*)k_pool; p.v_pool = (const __nv_bfloat16*)v_pool;
-  HFEE_REQUIRE(make_paged_cache(&p.cache, block_table, max_pages, page_size, kv_heads, head_dim),
+  HFEE_REQUIRE(make_paged_cache(&p.cache, block_table, max_pages, page_size, kv_heads, dist ? dist->key_dim : head_dim),
                "attention_mma: page_size %d must be a power of two", page_size);
+  make_paged_cache(&p.vcache, block_table, max_pages, page_size, kv_heads, dist ? dist->value_dim : head_dim);
+  p.dist_r1 = dist ? dist->r1 : nullptr; p.dist_r2 = dist ? dist->r2 : nullptr; p.out_scale = dist ? dist->out_scale : 1.f;
   p.cu_tokens = cu_tokens; p.slots = slots; p.context_before = context_before;
   p.heads = heads; p.group = group;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -652,6 +702,14 @@ int attention_mma_impl(const void* q, int ld_q, const void* k_pool, const void* 
     p.k_write = (__nv_bfloat16*)rope->k_write; p.v_write = (__nv_bfloat16*)rope->v_write;
   }
   int rc;
+  if (dist != nullptr) {
+    switch (head_dim) {
+#define HFEE_CASE(D) case D: rc = dispatch_mode<D, true>(p, ksplit, q_tiles, kv_heads, requests, stream); break;
+      HFEE_CASE(32) HFEE_CASE(64) HFEE_CASE(96) HFEE_CASE(128) HFEE_CASE(192) HFEE_CASE(256)
+#undef HFEE_CASE
+      default: return hfee_fail(HFEE_ERR_ARG, "attention_mma: tile size %d of the distance variant", head_dim);
+    }
+  } else
   switch (head_dim) {
 #define HFEE_CASE(D) case D: rc = dispatch_mode<D>(p, ksplit, q_tiles, kv_heads, requests, stream); break;
     HFEE_CASE(16) HFEE_CASE(32) HFEE_CASE(48) HFEE_CASE(64) HFEE_CASE(80) HFEE_CASE(96) HFEE_CASE(112) HFEE_CASE(128)
@@ -662,7 +720,8 @@ int attention_mma_impl(const void* q, int ld_q, const void* k_pool, const void* 
   if (rc != HFEE_OK || num_splits == 1) return rc;
   int pairs = n_tokens * heads;
   hfee_launch(attention_combine_kernel, dim3((unsigned)((pairs + COMBINE_WARPS - 1) / COMBINE_WARPS)),
-              dim3(COMBINE_WARPS * 32), 0, stream, p.part_o, p.part_ml, p.out, ld_o, heads, head_dim, num_splits, pairs);
+              dim3(COMBINE_WARPS * 32), 0, stream, p.part_o, p.part_ml, p.out, ld_o, heads, dist ? dist->value_dim : head_dim,
+              num_splits, pairs, head_dim, p.out_scale);
   return hfee_check_launch("attention_combine");
 }
 }  // namespace
@@ -678,6 +737,37 @@ HFEE_API int hfee_attention_mma(const void* q, int ld_q, const void* k_pool, con
   return attention_mma_impl(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, cu_tokens, slots, context_before,
                             out, ld_o, n_tokens, requests, max_new, heads, kv_heads, head_dim, scale, window, num_splits,
                             scratch, nullptr, stream);
+}
+
+// The tile size the distance variant uses for keys of key_dim and values of value_dim elements, or 0 when it does
+// not take them (both must be multiples of 8, at most 256).
+HFEE_API int hfee_attention_mma_distance_tile(int key_dim, int value_dim) {
+  if (key_dim <= 0 || value_dim <= 0 || key_dim % 8 || value_dim % 8) return 0;
+  const int need = key_dim > value_dim ? key_dim : value_dim;
+  const int sizes[] = {32, 64, 96, 128, 192, 256};
+  for (int s : sizes)
+    if (need <= s) return s;
+  return 0;
+}
+
+// hfee_attention_mma with keys of key_dim and values of value_dim elements (pools [num_pages, kv_heads, page_size,
+// key_dim] and [.., value_dim]; q [n_tokens, ld_q] holds heads * key_dim, out heads * value_dim per token), scores
+// q.k * scale - r1[h] * ln(1 + r2[h] * (query position - key position)) (r1, r2: float32 per query head), and
+// the output times out_scale.  Scratch for num_splits > 1: n_tokens * heads * num_splits * (tile + 2) floats with
+// tile = hfee_attention_mma_distance_tile(key_dim, value_dim).
+HFEE_API int hfee_attention_mma_distance(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                         const int* block_table, int max_pages, int page_size, const int* cu_tokens,
+                                         const int* slots, const int* context_before, void* out, int ld_o, int n_tokens,
+                                         int requests, int max_new, int heads, int kv_heads, int key_dim, int value_dim,
+                                         float scale, const float* r1, const float* r2, float out_scale, int window,
+                                         int num_splits, float* scratch, cudaStream_t stream) {
+  const int tile = hfee_attention_mma_distance_tile(key_dim, value_dim);
+  HFEE_REQUIRE(tile > 0, "attention_mma_distance: key size %d and value size %d must be multiples of 8 up to 256", key_dim, value_dim);
+  HFEE_REQUIRE(r1 != nullptr && r2 != nullptr, "attention_mma_distance: the penalty needs both of its arrays");
+  DistanceOption dist{key_dim, value_dim, r1, r2, out_scale};
+  return attention_mma_impl(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, cu_tokens, slots, context_before,
+                            out, ld_o, n_tokens, requests, max_new, heads, kv_heads, tile, scale, window, num_splits,
+                            scratch, nullptr, stream, &dist);
 }
 
 // A decode step (one new token per request) with the rotary kernel's work done inside: queries,

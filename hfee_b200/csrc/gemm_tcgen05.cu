@@ -57,7 +57,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_c, int reduce_by_tma,
                TOut* __restrict__ C, long long ldc, int M, int N, int K, int* __restrict__ status,
-               float* __restrict__ sk_parts, int* __restrict__ sk_flags, const RopeEpi rope) {
+               float* __restrict__ sk_parts, int* __restrict__ sk_flags, const RopeEpi rope,
+               const int* __restrict__ tile_group, int group_rows) {
   using Cfg = TileCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   constexpr uint32_t TMEM_COLS = ACC_STAGES * BN <= 256 ? 256 : 512;      // a power of two
@@ -80,12 +81,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const bool stream_k = sk_parts != nullptr;
   const long long total_units = (long long)total_tiles * k_blocks;
   auto range_begin = [&](long long cta) { return cta * total_units / (long long)gridDim.x; };
-  struct Walk { long long u, u_end; int t, stride, tiles, k_blocks; bool stream_k; };
+  // Grouped mode (tile_group != null, never with the split by K blocks): W holds one [N, K] matrix per group,
+  // stacked by rows; the rows of M tile i are multiplied with the matrix of group tile_group[i], and M tiles
+  // whose group is negative are left out by every role alike.
+  struct Walk { long long u, u_end; int t, stride, tiles, k_blocks; bool stream_k; const int* group; int m_tiles; };
   auto walk_start = [&]() {
     Walk w;
     w.stream_k = stream_k; w.k_blocks = k_blocks; w.tiles = total_tiles; w.stride = gridDim.x; w.t = blockIdx.x;
     w.u = stream_k ? range_begin(blockIdx.x) : 0;
     w.u_end = stream_k ? range_begin((long long)blockIdx.x + 1) : 0;
+    w.group = tile_group; w.m_tiles = m_tiles;
     return w;
   };
   auto walk_next = [](Walk& w, int& t, int& kb0, int& kb1) {
@@ -98,6 +103,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       w.u += kb1 - kb0;
       return true;
     }
+    if (w.group != nullptr)
+      while (w.t < w.tiles && w.group[w.t % w.m_tiles] < 0) w.t += w.stride;
     if (w.t >= w.tiles) return false;
     t = w.t; kb0 = 0; kb1 = w.k_blocks;
     w.t += w.stride;
@@ -131,7 +138,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     Walk w = walk_start();
     int t, kb0, kb1;
     while (ok && walk_next(w, t, kb0, kb1)) {
-      const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+      const int m0 = (t % m_tiles) * BM;
+      const int n0 = (t / m_tiles) * BN + (tile_group != nullptr ? tile_group[t % m_tiles] * group_rows : 0);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
         ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ((it / STAGES) & 1u) ^ 1u, &abort_flag));
@@ -423,7 +431,8 @@ int make_map_c(CUtensorMap* map, void* base, long long rows, long long cols, lon
 
 template <int BN, int EPI, typename TOut>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc, int M, int N, int K, int* status,
-           float* workspace, long long workspace_floats, int* flags, cudaStream_t stream, const RopeEpi& rope = RopeEpi{}) {
+           float* workspace, long long workspace_floats, int* flags, cudaStream_t stream, const RopeEpi& rope = RopeEpi{},
+           const int* tile_group = nullptr, int group_rows = 0) {
   using Cfg = TileCfg<BN>;
   // accumulate: by bulk tensor reduction when C can have a tensor map (16-byte aligned base and pitch)
   CUtensorMap mc = ma;
@@ -445,7 +454,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, long long ldc,
   const int sk_ctas = (workspace && flags) ? plan_stream_k(tiles, (K + BK - 1) / BK, sms, workspace_floats, BN) : 0;
   dim3 grid((unsigned)(sk_ctas ? sk_ctas : (tiles < sms ? tiles : sms)));          // one CTA per SM
   hfee_launch(gemm_tc_kernel<BN, EPI, TOut>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, ma, mw, mc, reduce_by_tma, (TOut*)C, ldc, M, N, K, status,
-              sk_ctas ? workspace : (float*)nullptr, sk_ctas ? flags : (int*)nullptr, rope);
+              sk_ctas ? workspace : (float*)nullptr, sk_ctas ? flags : (int*)nullptr, rope, tile_group, group_rows);
   return hfee_check_launch("gemm_tcgen05");
 }
 
@@ -499,6 +508,38 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
   if (block_n == 256) return dispatch<256>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, workspace, workspace_floats, flags, stream);
   if (block_n == 192) return dispatch<192>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, workspace, workspace_floats, flags, stream);
   return dispatch<128>(ma, mw, C, ldc, out_dtype, epilogue, M, N, K, status, workspace, workspace_floats, flags, stream);
+}
+
+// Grouped product: A [M, K] holds rows in tiles of 128 (M a multiple of 128), W [groups * N, K] one [N, K] matrix per
+// group stacked by rows; C[tile i's rows] = A[tile i's rows] . W[tile_group[i]]^T, tiles with a negative group are
+// left alone.  tile_group (device, M / 128 ints) is read by the kernel, so the launch does not depend on it.
+// C: bfloat16 or float32 [M, ldc], stored.
+HFEE_API int hfee_gemm_tcgen05_grouped(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
+                                       int out_dtype, int M, int N, int K, int groups, const int* tile_group, int* status,
+                                       cudaStream_t stream) {
+  if (M == 0 || N == 0) return HFEE_OK;
+  HFEE_REQUIRE(M > 0 && M % BM == 0 && N > 0 && K > 0 && K % 8 == 0 && groups > 0 && tile_group != nullptr,
+               "gemm_tcgen05_grouped: M=%d must be a multiple of 128 and K=%d a multiple of 8", M, K);
+  HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K && ldc >= N,
+               "gemm_tcgen05_grouped: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
+  HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05_grouped: operands must be 16-byte aligned");
+  HFEE_REQUIRE((long long)groups * N < (1ll << 31), "gemm_tcgen05_grouped: too many rows of W");
+  const int sms = hfee_sm_count();
+  // tiles of 256 columns when those still give every SM one (few rows per group: the W tiles are the traffic)
+  const int bn = (long long)(M / BM) * ((N + 255) / 256) >= (sms > 0 ? sms : 148) ? 256 : 128;
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, BM);
+  if (rc != HFEE_OK) return rc;
+  rc = make_map(&mw, W, (long long)groups * N, K, ldw, bn);
+  if (rc != HFEE_OK) return rc;
+  if (bn == 256) {
+    if (out_dtype == HFEE_BF16)
+      return launch<256, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, RopeEpi{}, tile_group, N);
+    return launch<256, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, RopeEpi{}, tile_group, N);
+  }
+  if (out_dtype == HFEE_BF16)
+    return launch<128, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, RopeEpi{}, tile_group, N);
+  return launch<128, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, RopeEpi{}, tile_group, N);
 }
 
 // How many CTAs hfee_gemm_tcgen05 would split this shape's K blocks among (0: whole tiles per CTA).

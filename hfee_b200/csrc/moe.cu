@@ -10,6 +10,12 @@
 //   hfee_moe_down      pair_out[sorted[place]] = W_down[e] hidden[place] (float32).
 //   hfee_moe_combine   y[t] (+)= sum_k weight[t, k] * pair_out[t * top + k].
 //
+// For the tensor cores the places are laid out in tiles of as many rows as a product's tile has, every expert
+// starting at a tile's border (hfee_moe_plan_tiles), the tokens' rows are copied to their places
+// (hfee_moe_gather_rows), the two products run as grouped products over those tiles (each tile against its expert's
+// matrix), and hfee_moe_combine finds a pair's row through place_of_pair.  Rows between an expert's last pair and
+// the next border hold whatever the buffer held; a row of a product depends on that row alone, and nothing reads them.
+//
 // Everything the launches depend on (grids, buffers) follows from the number of tokens alone; counts and places
 // live in device memory, so a step replays from a CUDA graph.  A pair's result is computed by one thread block
 // with k summed in order and does not depend on its place, so the order inside an expert (which the plan's atomic
@@ -102,6 +108,56 @@ moe_plan_kernel(const int* __restrict__ choice, int pairs, int experts, int* __r
   }
 }
 
+// Places in tiles of tile_rows rows: expert e's pairs lie from first_tile[e] * tile_rows on.  place_of_pair[pair] is the
+// pair's row, row_pair[row] the pair of a row (-1: none), tile_group[tile] the tile's expert (-1: unused).
+__global__ void __launch_bounds__(PLAN_THREADS)
+moe_plan_tiles_kernel(const int* __restrict__ choice, int pairs, int experts, int tile_rows, int* __restrict__ place_of_pair,
+                      int* __restrict__ row_pair, int* __restrict__ tile_group, int max_tiles) {
+  __shared__ int count[MAX_EXPERTS], cursor[MAX_EXPERTS], first_tile[MAX_EXPERTS + 1];
+  for (int e = threadIdx.x; e < experts; e += PLAN_THREADS) count[e] = cursor[e] = 0;
+  pdl_wait();
+  pdl_launch_dependents();
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += PLAN_THREADS) atomicAdd(&count[choice[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tile = 0;
+    for (int e = 0; e < experts; ++e) {
+      first_tile[e] = tile;
+      tile += (count[e] + tile_rows - 1) / tile_rows;
+    }
+    first_tile[experts] = tile;
+  }
+  __syncthreads();
+  const int used = first_tile[experts];
+  for (int e = threadIdx.x; e < experts; e += PLAN_THREADS)
+    for (int j = first_tile[e]; j < first_tile[e + 1]; ++j) tile_group[j] = e;
+  for (int j = used + threadIdx.x; j < max_tiles; j += PLAN_THREADS) tile_group[j] = -1;
+  for (long long r = threadIdx.x; r < (long long)used * tile_rows; r += PLAN_THREADS) row_pair[r] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += PLAN_THREADS) {
+    const int e = choice[i];
+    const int row = first_tile[e] * tile_rows + atomicAdd(&cursor[e], 1);
+    place_of_pair[i] = row;
+    row_pair[row] = i;
+  }
+}
+
+// xg[row] = x[row_pair[row] / top] for the rows of used tiles that hold a pair; 16 bytes per thread and step.
+__global__ void __launch_bounds__(128)
+moe_gather_rows_kernel(const uint4* __restrict__ x, long long ld_x16, int top, const int* __restrict__ row_pair,
+                       const int* __restrict__ tile_group, int tile_rows, uint4* __restrict__ xg, long long ld_g16, int width16) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  if (tile_group[row / tile_rows] < 0) return;
+  const int pair = row_pair[row];
+  if (pair < 0) return;
+  const uint4* src = x + (long long)(pair / top) * ld_x16;
+  uint4* dst = xg + (long long)row * ld_g16;
+  for (int i = threadIdx.x; i < width16; i += 128) dst[i] = src[i];
+}
+
 __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
   const float g = fminf(gate, limit);
   const float u = fminf(fmaxf(up, -limit), limit);
@@ -185,14 +241,17 @@ moe_expert_kernel(const T* __restrict__ a, long long ld_a, int top, const T* __r
 }
 
 __global__ void __launch_bounds__(THREADS)
-moe_combine_kernel(const float* __restrict__ pair_out, const float* __restrict__ weight, int top, float* __restrict__ y, int width,
-                   int accumulate) {
+moe_combine_kernel(const float* __restrict__ pair_out, const float* __restrict__ weight, const int* __restrict__ place, int top,
+                   float* __restrict__ y, int width, int accumulate) {      // place: the row of each pair (null: the pair's index)
   pdl_wait();
   pdl_launch_dependents();
   const long long t = blockIdx.x;
   for (int c = threadIdx.x; c < width; c += THREADS) {
     float acc = accumulate ? y[t * width + c] : 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(weight[t * top + k], pair_out[(t * top + k) * width + c], acc);
+    for (int k = 0; k < top; ++k) {
+      const long long row = place ? place[t * top + k] : t * top + k;
+      acc = fmaf(weight[t * top + k], pair_out[row * width + c], acc);
+    }
     y[t * width + c] = acc;
   }
 }
@@ -238,16 +297,18 @@ HFEE_API int hfee_moe_plan(const int* choice, int pairs, int experts, int* offse
 }
 
 // x: [n, width] tokens; w_gate, w_up: [experts, inner, width]; hidden: [pairs, inner] by place.
-HFEE_API int hfee_moe_gate_up(const void* x, long long ld_x, int top, const void* w_gate, const void* w_up, int inner, int width,
-                              const int* offsets, const int* sorted, const int* tile_expert, const int* tile_row, void* hidden,
+// expert_stride: elements from one expert's w_gate (and w_up) to the next one's.
+HFEE_API int hfee_moe_gate_up(const void* x, long long ld_x, int top, const void* w_gate, const void* w_up, long long expert_stride,
+                              int inner, int width, const int* offsets, const int* sorted, const int* tile_expert, const int* tile_row, void* hidden,
                               long long ld_hidden, float limit, float alpha, int max_tiles, int dtype, cudaStream_t stream) {
   if (max_tiles == 0) return HFEE_OK;
-  HFEE_REQUIRE(inner > 0 && width > 0 && top > 0 && ld_x >= width && ld_hidden >= inner && limit > 0.f, "moe_gate_up: bad sizes");
+  HFEE_REQUIRE(inner > 0 && width > 0 && top > 0 && ld_x >= width && ld_hidden >= inner && limit > 0.f &&
+               expert_stride >= (long long)inner * width, "moe_gate_up: bad sizes");
   if (dtype == HFEE_F32)
-    return launch_experts<float>(true, x, ld_x, top, w_gate, w_up, (long long)inner * width, inner, width, offsets, sorted, tile_expert,
+    return launch_experts<float>(true, x, ld_x, top, w_gate, w_up, expert_stride, inner, width, offsets, sorted, tile_expert,
                                  tile_row, hidden, nullptr, ld_hidden, limit, alpha, max_tiles, stream);
   if (dtype == HFEE_BF16)
-    return launch_experts<__nv_bfloat16>(true, x, ld_x, top, w_gate, w_up, (long long)inner * width, inner, width, offsets, sorted,
+    return launch_experts<__nv_bfloat16>(true, x, ld_x, top, w_gate, w_up, expert_stride, inner, width, offsets, sorted,
                                          tile_expert, tile_row, hidden, nullptr, ld_hidden, limit, alpha, max_tiles, stream);
   return hfee_fail(HFEE_ERR_ARG, "moe_gate_up: unknown dtype %d", dtype);
 }
@@ -267,10 +328,33 @@ HFEE_API int hfee_moe_down(const void* hidden, long long ld_hidden, int top, con
   return hfee_fail(HFEE_ERR_ARG, "moe_down: unknown dtype %d", dtype);
 }
 
-HFEE_API int hfee_moe_combine(const float* pair_out, const float* weight, int n, int top, float* y, int width, int accumulate,
-                              cudaStream_t stream) {
+HFEE_API int hfee_moe_combine(const float* pair_out, const float* weight, const int* place, int n, int top, float* y, int width,
+                              int accumulate, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && top > 0 && width > 0, "moe_combine: bad sizes");
-  hfee_launch(moe_combine_kernel, dim3(n), dim3(THREADS), 0, stream, pair_out, weight, top, y, width, accumulate);
+  hfee_launch(moe_combine_kernel, dim3(n), dim3(THREADS), 0, stream, pair_out, weight, place, top, y, width, accumulate);
   return hfee_check_launch("moe_combine");
+}
+
+// place_of_pair: [pairs]; row_pair: [max_tiles * tile_rows]; tile_group: [max_tiles], max_tiles >= pairs / tile_rows +
+// min(experts, pairs).
+HFEE_API int hfee_moe_plan_tiles(const int* choice, int pairs, int experts, int tile_rows, int* place_of_pair, int* row_pair,
+                                 int* tile_group, int max_tiles, cudaStream_t stream) {
+  if (pairs == 0) return HFEE_OK;
+  HFEE_REQUIRE(pairs > 0 && experts >= 1 && experts <= MAX_EXPERTS && tile_rows > 0, "moe_plan_tiles: bad sizes");
+  HFEE_REQUIRE(max_tiles >= pairs / tile_rows + (experts < pairs ? experts : pairs), "moe_plan_tiles: room for %d tiles is too little", max_tiles);
+  hfee_launch(moe_plan_tiles_kernel, dim3(1), dim3(PLAN_THREADS), 0, stream, choice, pairs, experts, tile_rows, place_of_pair, row_pair,
+              tile_group, max_tiles);
+  return hfee_check_launch("moe_plan_tiles");
+}
+
+// x: [n, width] tokens; xg: [max_tiles * tile_rows, width] by place.  16-bit elements, rows of whole 16-byte pieces.
+HFEE_API int hfee_moe_gather_rows(const void* x, long long ld_x, int top, const int* row_pair, const int* tile_group, int tile_rows,
+                                  void* xg, long long ld_g, int width, int max_tiles, cudaStream_t stream) {
+  if (max_tiles == 0) return HFEE_OK;
+  HFEE_REQUIRE(width > 0 && width % 8 == 0 && ld_x % 8 == 0 && ld_g % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)xg % 16 == 0),
+               "moe_gather_rows: rows must be whole 16-byte pieces");
+  hfee_launch(moe_gather_rows_kernel, dim3((unsigned)(max_tiles * tile_rows)), dim3(128), 0, stream, (const uint4*)x, ld_x / 8, top,
+              row_pair, tile_group, tile_rows, (uint4*)xg, ld_g / 8, width / 8);
+  return hfee_check_launch("moe_gather_rows");
 }

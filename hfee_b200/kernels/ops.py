@@ -72,6 +72,9 @@ _SIGNATURES = {
     "hfee_conv_act": [_P, _L, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     "hfee_attention_simt_distance": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _L, _I,
                                      _P, _P, _F, _I, _P],
+    "hfee_attention_mma_distance": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _F, _I, _I,
+                                    _P, _P],
+    "hfee_attention_mma_distance_tile": [_I, _I],
     "hfee_add_sinusoid": [_P, _P, _I, _I, _F, _P],
     "hfee_softcap": [_P, _L, _I, _I, _F, _P],
     "hfee_clamped_glu": [_P, _L, _P, _L, _I, _I, _I, _F, _F, _I, _P],
@@ -81,9 +84,12 @@ _SIGNATURES = {
     "hfee_selective_scan": [_P, _L, _P, _L, _P, _L, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _F, _I, _I, _P],
     "hfee_moe_route": [_P, _I, _I, _I, _F, _P, _P, _P],
     "hfee_moe_plan": [_P, _I, _I, _P, _P, _P, _P, _I, _P],
-    "hfee_moe_gate_up": [_P, _L, _I, _P, _P, _I, _I, _P, _P, _P, _P, _P, _L, _F, _F, _I, _I, _P],
+    "hfee_moe_gate_up": [_P, _L, _I, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _L, _F, _F, _I, _I, _P],
     "hfee_moe_down": [_P, _L, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P],
-    "hfee_moe_combine": [_P, _P, _I, _I, _P, _I, _I, _P],
+    "hfee_moe_combine": [_P, _P, _P, _I, _I, _P, _I, _I, _P],
+    "hfee_moe_plan_tiles": [_P, _I, _I, _I, _P, _P, _P, _I, _P],
+    "hfee_moe_gather_rows": [_P, _L, _I, _P, _P, _I, _P, _L, _I, _I, _P],
+    "hfee_gemm_tcgen05_grouped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _P, _P],
     "hfee_conv_act_launches": [_I, _I, _I],
     "hfee_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P],
     "hfee_head_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
@@ -1013,12 +1019,55 @@ def attention_simt_distance(q, k_pool, v_pool, block_table, page_size, positions
                                             GATE_NONE, r1.data_ptr(), r2.data_ptr(), float(out_scale), _dt(q), _stream()), lib)
 
 
+DISTANCE_ATTENTION_ON_TENSOR_CORES = True
+_DISTANCE_TILE: dict = {}
+
+
+def distance_attention_tile(head_dim: int, value_dim: int) -> int:
+    """Tile size (floats per partial output) of the tensor-core kernel for these key and value sizes; 0: it does not
+    take them."""
+    key = (head_dim, value_dim)
+    if key not in _DISTANCE_TILE:
+        _DISTANCE_TILE[key] = int(library().hfee_attention_mma_distance_tile(head_dim, value_dim))
+    return _DISTANCE_TILE[key]
+
+
 def distance_attention(q, k_pool, v_pool, block_table, page_size, step, out, heads, kv_heads, head_dim, value_dim, scale, r1, r2,
-                       out_scale=1.0, window=0) -> None:
+                       out_scale=1.0, window=0, scratch=None) -> None:
     """Causal grouped-query softmax attention over the paged cache whose scores lose ``r1[h] * ln(1 + r2[h] * distance)``,
-    choosing the kernel for the dtype and the step."""
-    attention_simt_distance(q, k_pool, v_pool, block_table, page_size, step.positions, step.slot_of_token, out, heads, kv_heads,
-                            head_dim, value_dim, scale, r1, r2, out_scale, window)
+    choosing the kernel for the dtype and the step: bfloat16 with key and value sizes that are multiples of 8 (up to 256)
+    runs on the tensor cores (prompt portions, decode steps with their keys split among CTAs when ``scratch`` is given,
+    and mixtures), everything else on the CUDA cores in float32 arithmetic."""
+    group = heads // kv_heads
+    tile = distance_attention_tile(head_dim, value_dim) if (DISTANCE_ATTENTION_ON_TENSOR_CORES and q.dtype == torch.bfloat16) else 0
+    if not (tile and group <= 64 and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0 and _rows(out, "out") % 4 == 0
+            and out.data_ptr() % 8 == 0):
+        attention_simt_distance(q, k_pool, v_pool, block_table, page_size, step.positions, step.slot_of_token, out, heads, kv_heads,
+                                head_dim, value_dim, scale, r1, r2, out_scale, window)
+        return
+    lib = library()
+    for t, what in ((block_table, "block_table"), (step.cu_tokens, "cu_tokens"), (step.slots, "slots"),
+                    (step.context_before, "context_before")):
+        _i32(t, what)
+    assert k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16 and k_pool.is_contiguous() and v_pool.is_contiguous()
+    assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim) and tuple(v_pool.shape[1:]) == (kv_heads, page_size, value_dim)
+    assert q.shape[1] == heads * head_dim and tuple(out.shape) == (step.n, heads * value_dim)
+    for r in (r1, r2):
+        assert r.dtype == torch.float32 and r.is_contiguous() and r.numel() == heads
+    splits = 1
+    if step.max_new * group <= 16 and scratch is not None:
+        splits = getattr(step, "attention_splits", None) or attention_splits(
+            step.r, kv_heads, getattr(step, "planning_context", step.max_context))
+        if step.n * heads * splits * (tile + 2) > scratch.numel():
+            splits = 1
+    _check(lib.hfee_attention_mma_distance(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
+                                           block_table.shape[1], page_size, step.cu_tokens.data_ptr(), step.slots.data_ptr(),
+                                           step.context_before.data_ptr(), out.data_ptr(), _rows(out, "attention out"), step.n,
+                                           step.r, step.max_new, heads, kv_heads, head_dim, value_dim, float(scale), r1.data_ptr(),
+                                           r2.data_ptr(), float(out_scale), int(window or 0), splits,
+                                           _ptr(scratch) if splits > 1 else None, _stream()), lib)
+    if splits > 1:
+        count_launches(1)
 
 
 # The grouped-query kernels on the tensor cores take bfloat16 queries and keys and round the softmax weights to
@@ -1437,12 +1486,14 @@ def moe_experts(x: torch.Tensor, top: int, w_gate: torch.Tensor, w_up: torch.Ten
     experts, inner = w_gate.shape[0], w_gate.shape[1]
     pairs = n * top
     tiles = min(tile_expert.numel(), moe_max_tiles(pairs, experts))
-    assert w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
+    # gate and up may be the two halves of one [experts, 2 * inner, width] tensor: each expert's matrix dense, one stride
+    assert w_down.is_contiguous() and w_gate.stride() == w_up.stride() and w_gate.stride()[1:] == (width, 1)
     assert tuple(w_up.shape) == (experts, inner, width) and tuple(w_down.shape) == (experts, width, inner)
     assert x.dtype == w_gate.dtype == w_up.dtype == w_down.dtype == hidden.dtype
     assert hidden.shape[0] >= pairs and hidden.shape[1] == inner
     assert pair_out.dtype == torch.float32 and pair_out.is_contiguous() and pair_out.shape[0] >= pairs and pair_out.shape[1] == width
-    _check(lib.hfee_moe_gate_up(x.data_ptr(), _rows(x, "x"), top, w_gate.data_ptr(), w_up.data_ptr(), inner, width, offsets.data_ptr(),
+    _check(lib.hfee_moe_gate_up(x.data_ptr(), _rows(x, "x"), top, w_gate.data_ptr(), w_up.data_ptr(), w_gate.stride(0), inner, width,
+                                offsets.data_ptr(),
                                 order.data_ptr(), tile_expert.data_ptr(), tile_row.data_ptr(), hidden.data_ptr(),
                                 _rows(hidden, "hidden"), float(limit), float(alpha), tiles, _dt(x), _stream()), lib)
     _check(lib.hfee_moe_down(hidden.data_ptr(), _rows(hidden, "hidden"), top, w_down.data_ptr(), inner, width, offsets.data_ptr(),
@@ -1450,12 +1501,76 @@ def moe_experts(x: torch.Tensor, top: int, w_gate: torch.Tensor, w_up: torch.Ten
                              _stream()), lib)
 
 
-def moe_combine(pair_out: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, accumulate: bool) -> None:
-    """y[t] (+)= sum_k weight[t, k] * pair_out[t * top + k] (float32)."""
+def moe_combine(pair_out: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, accumulate: bool,
+                place: Optional[torch.Tensor] = None) -> None:
+    """y[t] (+)= sum_k weight[t, k] * pair_out[row of pair t * top + k] (float32); the row is ``place[pair]``, or the
+    pair's index without ``place``."""
     lib = library()
     n, top = weight.shape
     assert y.dtype == torch.float32 and y.is_contiguous() and y.shape[0] == n and pair_out.shape[1] == y.shape[1]
-    _check(lib.hfee_moe_combine(pair_out.data_ptr(), weight.data_ptr(), n, top, y.data_ptr(), y.shape[1], int(accumulate), _stream()), lib)
+    assert pair_out.dtype == torch.float32 and pair_out.is_contiguous()
+    if place is not None:
+        _i32(place, "place")
+        assert place.numel() >= n * top
+    _check(lib.hfee_moe_combine(pair_out.data_ptr(), weight.data_ptr(), _ptr(place), n, top, y.data_ptr(), y.shape[1], int(accumulate),
+                                _stream()), lib)
+
+
+GROUPED_TILE_ROWS = 128         # rows of a tile of the grouped product
+
+
+def moe_tiles_grouped(pairs: int, experts: int) -> int:
+    """Tiles of GROUPED_TILE_ROWS rows that ``pairs`` pairs over ``experts`` experts can need when every expert starts at
+    a tile's border: an expert with c pairs fills c // 128 tiles and at most one more, and no more experts have pairs
+    than there are pairs."""
+    return pairs // GROUPED_TILE_ROWS + min(experts, pairs)
+
+
+def moe_experts_grouped_ok(x_dtype: torch.dtype, width: int, inner: int) -> bool:
+    """Whether :func:`moe_experts_grouped` takes these: bfloat16, rows of whole 16-byte pieces."""
+    return x_dtype == torch.bfloat16 and width % 8 == 0 and inner % 8 == 0
+
+
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor) -> None:
+    """out[rows of tile i] = a[rows of tile i] @ w[tile_group[i]].T for tiles of GROUPED_TILE_ROWS rows; tiles whose
+    group is negative are left alone.  ``a`` [tiles * 128, k] bfloat16, ``w`` [groups, n, k] bfloat16 contiguous,
+    ``out`` [tiles * 128, n] bfloat16 or float32.  ``tile_group`` is read on the device."""
+    lib = library()
+    m, k = a.shape
+    groups, n = w.shape[0], w.shape[1]
+    _i32(tile_group, "tile_group")
+    assert w.shape[2] == k and w.is_contiguous() and a.dtype == w.dtype == torch.bfloat16
+    assert m % GROUPED_TILE_ROWS == 0 and tile_group.numel() >= m // GROUPED_TILE_ROWS and tuple(out.shape) == (m, n)
+    _check(lib.hfee_gemm_tcgen05_grouped(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), k, out.data_ptr(), _rows(out, "gemm out"),
+                                         _dt(out), m, n, k, groups, tile_group.data_ptr(), _status().data_ptr(), _stream()), lib)
+
+
+def moe_experts_grouped(x: torch.Tensor, top: int, choice: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float,
+                        place: torch.Tensor, row_pair: torch.Tensor, tile_group: torch.Tensor, rows_in: torch.Tensor,
+                        gate_up: torch.Tensor, hidden: torch.Tensor, rows_out: torch.Tensor,
+                        alpha: float = CLAMPED_SWISH_ALPHA) -> None:
+    """The experts' two products on the tensor cores: rows_out[place[pair]] = W_down[e] act(W_gate[e] x, W_up[e] x) for every
+    (token, chosen expert e) pair, float32.  ``w_gate_up`` [experts, 2 * inner, width] holds each expert's gate rows, then
+    its up rows; ``w_down`` [experts, width, inner].  Scratch, all of ``tiles * 128`` rows with ``tiles =
+    moe_tiles_grouped(pairs, experts)``: ``rows_in`` [., width], ``gate_up`` [., 2 * inner], ``hidden`` [., inner]
+    (bfloat16), ``rows_out`` [., width] float32; ``place`` [pairs], ``row_pair`` [tiles * 128], ``tile_group`` [tiles]."""
+    lib = library()
+    n, width = x.shape
+    experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    pairs = n * top
+    tiles = moe_tiles_grouped(pairs, experts)
+    rows = tiles * GROUPED_TILE_ROWS
+    for t in (choice, place, row_pair, tile_group):
+        _i32(t, "moe plan")
+    assert choice.numel() == pairs and place.numel() >= pairs and row_pair.numel() >= rows and tile_group.numel() >= tiles
+    assert rows_in.shape[0] >= rows and gate_up.shape[0] >= rows and hidden.shape[0] >= rows and rows_out.shape[0] >= rows
+    _check(lib.hfee_moe_plan_tiles(choice.data_ptr(), pairs, experts, GROUPED_TILE_ROWS, place.data_ptr(), row_pair.data_ptr(),
+                                   tile_group.data_ptr(), tiles, _stream()), lib)
+    _check(lib.hfee_moe_gather_rows(x.data_ptr(), _rows(x, "x"), top, row_pair.data_ptr(), tile_group.data_ptr(), GROUPED_TILE_ROWS,
+                                    rows_in.data_ptr(), _rows(rows_in, "rows_in"), width, tiles, _stream()), lib)
+    gemm_tcgen05_grouped(rows_in[:rows], w_gate_up, tile_group, gate_up[:rows])
+    clamped_glu(gate_up[:rows], hidden[:rows], limit, alpha)
+    gemm_tcgen05_grouped(hidden[:rows], w_down, tile_group, rows_out[:rows])
 
 
 def qk_norm_rope_cache(qk: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,

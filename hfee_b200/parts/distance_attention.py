@@ -43,6 +43,10 @@ class DistanceAttention(SplitMixer):
         self.r1, self.r2 = tensors["r1"], tensors["r2"]
         self.w_o = tensors["o"]
         self.inner_cols, self.in_rows = self.heads * self.value_dim, self.q_cols + self.k_cols + self.v_cols
+        # partial results of a decode step whose keys are split among CTAs (tensor-core kernel only)
+        tile = ops.distance_attention_tile(self.head_dim, self.value_dim) if rt.dtype == torch.bfloat16 else 0
+        self.split_scratch = rt.scratch("attn_partials", (rt.max_requests * self.heads * ops.MAX_SPLITS * (tile + 2),),
+                                        torch.float32) if tile else None
 
     def cache_need(self) -> PagedKV:
         return PagedKV(self.kv_heads, self.head_dim, self.window, None, self.value_dim)
@@ -56,7 +60,8 @@ class DistanceAttention(SplitMixer):
                                 v=(self.q_cols + self.k_cols, vd, vd, cache.v))
         ops.tag("attention")
         ops.distance_attention(proj[:, :self.q_cols], cache.k, cache.v, cache.block_table, cache.page_size, step, into,
-                               self.heads, self.kv_heads, d, vd, self.scale, self.r1, self.r2, out_scale, int(self.window or 0))
+                               self.heads, self.kv_heads, d, vd, self.scale, self.r1, self.r2, out_scale, int(self.window or 0),
+                               self.split_scratch)
 
 
 register_part("mixer", "distance_attention", DistanceAttention)

@@ -4,9 +4,11 @@
     out = sum_(e in chosen) router_scale * s_e * expert_e(h)  +  shared(h)
     expert(h) = W_down (g * sigmoid(alpha * g) * (u + 1)),  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
 
-The chosen weights are not renormalised.  The experts' tensors are stacked at load time (``[experts, inner, width]``
-twice and ``[experts, width, inner]``); the (token, choice) pairs are ordered by expert on the device, so the launches
-of a step depend on its token count alone and the step replays from a CUDA graph.
+The chosen weights are not renormalised.  The experts' tensors are stacked at load time (``[experts, 2 * inner, width]``,
+each expert's gate rows and then its up rows, and ``[experts, width, inner]``); the (token, choice) pairs are ordered by
+expert on the device, so the launches of a step depend on its token count alone and the step replays from a CUDA graph.
+In bfloat16 with rows of whole 16-byte pieces the two products run on the tensor cores as grouped products over tiles of
+128 places that never span two experts; otherwise (float32) on the CUDA cores in tiles of 32 places.
 """
 from __future__ import annotations
 
@@ -49,8 +51,9 @@ class RoutedExperts(Part):
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"top {self.top} is outside 1..{self.experts}")
         self.w_router = tensors["router"]
-        self.w_gate = torch.stack([tensors[f"e{e}.gate"] for e in range(self.experts)]).contiguous()
-        self.w_up = torch.stack([tensors[f"e{e}.up"] for e in range(self.experts)]).contiguous()
+        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                      for e in range(self.experts)]).contiguous()
+        self.w_gate, self.w_up = self.w_gate_up[:, :self.inner], self.w_gate_up[:, self.inner:]
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
         self.shared_inner = spec.get("shared_inner")
         if self.shared_inner is not None:
@@ -58,7 +61,8 @@ class RoutedExperts(Part):
             self.w_shared_in = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0).contiguous()
             self.w_shared_down = tensors["shared.down"]
         pairs = rt.max_tokens * self.top
-        self.tiles = ops.moe_max_tiles(pairs, self.experts)
+        self.grouped = ops.moe_experts_grouped_ok(rt.dtype, self.width, self.inner)
+        self.tiles = ops.moe_tiles_grouped(pairs, self.experts) if self.grouped else ops.moe_max_tiles(pairs, self.experts)
 
     def forward(self, xn, out: torch.Tensor, step: Any, accumulate: bool = True) -> None:
         n, rt, top = step.n, self.rt, self.top
@@ -67,19 +71,33 @@ class RoutedExperts(Part):
         logits = rt.scratch("moe_logits", (rt.max_tokens, self.experts), torch.float32)[:n]
         choice = rt.scratch("moe_choice", (rt.max_tokens, top), i32)[:n]
         weight = rt.scratch("moe_weight", (rt.max_tokens, top), torch.float32)[:n]
-        offsets = rt.scratch("moe_offsets", (self.experts + 1,), i32)
-        order = rt.scratch("moe_order", (rt.max_tokens * top,), i32)
-        tile_expert = rt.scratch("moe_tile_expert", (self.tiles,), i32)
-        tile_row = rt.scratch("moe_tile_row", (self.tiles,), i32)
-        hidden = rt.scratch("moe_hidden", (rt.max_tokens * top, pad8(self.inner)))[:n * top, :self.inner]
-        pair_out = rt.scratch("moe_pair_out", (rt.max_tokens * top, self.width), torch.float32)[:n * top]
         ops.tag("router")
         ops.linear(xn, self.w_router, logits)
         ops.moe_route(logits, top, self.router_scale, choice, weight)
-        ops.moe_plan(choice, self.experts, offsets, order, tile_expert, tile_row)
-        ops.tag("experts")
-        ops.moe_experts(xn, top, self.w_gate, self.w_up, self.w_down, self.limit, offsets, order, tile_expert, tile_row,
-                        hidden, pair_out, self.alpha)
+        place = None
+        if self.grouped:
+            rows = self.tiles * ops.GROUPED_TILE_ROWS
+            place = rt.scratch("moe_place", (rt.max_tokens * top,), i32)
+            row_pair = rt.scratch("moe_row_pair", (rows,), i32)
+            tile_group = rt.scratch("moe_tile_group", (self.tiles,), i32)
+            rows_in = rt.scratch("moe_rows_in", (rows, self.width))
+            gate_up = rt.scratch("moe_gate_up", (rows, 2 * self.inner))
+            hidden = rt.scratch("moe_hidden_rows", (rows, self.inner))
+            pair_out = rt.scratch("moe_rows_out", (rows, self.width), torch.float32)
+            ops.tag("experts")
+            ops.moe_experts_grouped(xn, top, choice, self.w_gate_up, self.w_down, self.limit, place, row_pair, tile_group,
+                                    rows_in, gate_up, hidden, pair_out, self.alpha)
+        else:
+            offsets = rt.scratch("moe_offsets", (self.experts + 1,), i32)
+            order = rt.scratch("moe_order", (rt.max_tokens * top,), i32)
+            tile_expert = rt.scratch("moe_tile_expert", (self.tiles,), i32)
+            tile_row = rt.scratch("moe_tile_row", (self.tiles,), i32)
+            hidden = rt.scratch("moe_hidden", (rt.max_tokens * top, pad8(self.inner)))[:n * top, :self.inner]
+            pair_out = rt.scratch("moe_pair_out", (rt.max_tokens * top, self.width), torch.float32)[:n * top]
+            ops.moe_plan(choice, self.experts, offsets, order, tile_expert, tile_row)
+            ops.tag("experts")
+            ops.moe_experts(xn, top, self.w_gate, self.w_up, self.w_down, self.limit, offsets, order, tile_expert, tile_row,
+                            hidden, pair_out, self.alpha)
         if self.shared_inner is not None:
             s = self.shared_inner
             gu = rt.scratch("ffn_gate_up", (rt.max_tokens, pad8(2 * s)))[:n, :2 * s]
@@ -91,7 +109,7 @@ class RoutedExperts(Part):
             ops.linear(h, self.w_shared_down, out, accumulate=accumulate)
             accumulate = True
         ops.tag("experts")
-        ops.moe_combine(pair_out, weight, out, accumulate)
+        ops.moe_combine(pair_out, weight, out, accumulate, place)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

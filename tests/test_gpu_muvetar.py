@@ -150,7 +150,7 @@ def test_distance_penalty_and_page_edges(tmp_path, dtype):
     seq = mu.sequences(60, (100,), seed=2)[0]
     ref = plain.forward(c, w, seq)
     for name, change in (("l0.mix.left.r1", lambda v: v * 1.05), ("l0.mix.left.r2", lambda v: v * 1.1), ("l0.mix.left.r1", lambda v: v * 0.0)):
-        assert ru.rel_err(plain.forward(c, {**w, name: change(w[name])}, seq)[1:], ref[1:]) > 5 * TOL[dtype]
+        assert ru.rel_err(plain.forward(c, {**w, name: change(w[name])}, seq)[1:], ref[1:]) > 5 * TOL["float32"]
     cuts = [(100,), (page, page, 100), (page - 1, 2, page - 1, 2, 100), (page + 1, page - 1, 2, 100),
             (47,) + (1,) * 53, (15,) + (1,) * 85, (2, 2, 100), (1, 1, 1, 100)]
     for sizes in cuts:

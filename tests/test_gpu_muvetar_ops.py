@@ -245,3 +245,147 @@ def test_clamped_gate(inner, dtype):
     v = gu.double().cpu().numpy()
     g, u = np.minimum(v[:, :inner], 1.5), np.clip(v[:, inner:], -1.5, 1.5)
     assert close(out.float().cpu().numpy(), g / (1 + np.exp(-1.702 * g)) * (u + 1), 2e-6 if dtype == torch.float32 else 8e-3)
+
+
+class DistanceBatch:
+    """A paged cache with shuffled pages, keys of ``d`` and values of ``dv`` elements, stale content in the unused places,
+    and a step of ``new[i]`` tokens for request i with ``before[i]`` tokens cached."""
+
+    def __init__(self, dtype, heads, kv, d, dv, page, before, new, seed=0):
+        g = torch.Generator().manual_seed(seed)
+        r = len(before)
+        total = [b + n for b, n in zip(before, new)]
+        max_pages = max(-(-t // page) for t in total) + 1
+        n_pages = r * max_pages + 2
+        perm = torch.randperm(n_pages, generator=g)[:r * max_pages].reshape(r, max_pages)
+        self.block_table = perm.to(torch.int32).to(DEV)
+        self.kp = (torch.randn(n_pages, kv, page, d, generator=g) * 30).to(dtype).to(DEV)
+        self.vp = (torch.randn(n_pages, kv, page, dv, generator=g) * 30).to(dtype).to(DEV)
+        self.k = [torch.randn(t, kv, d, generator=g).to(dtype) for t in total]
+        self.v = [torch.randn(t, kv, dv, generator=g).to(dtype) for t in total]
+        for i in range(r):
+            for first in range(0, total[i], page):
+                pg, m = int(perm[i, first // page]), min(page, total[i] - first)
+                self.kp[pg, :, :m] = self.k[i][first:first + m].transpose(0, 1).to(DEV)
+                self.vp[pg, :, :m] = self.v[i][first:first + m].transpose(0, 1).to(DEV)
+        self.n, self.r, self.before, self.new = sum(new), r, before, new
+        self.q = (torch.randn(self.n, heads * d, generator=g) * 1.5).to(dtype).to(DEV)
+        i32 = lambda x: torch.tensor(np.asarray(x), dtype=torch.int32, device=DEV)
+        self.cu_tokens, self.slots, self.context_before = i32(np.concatenate([[0], np.cumsum(new)])), i32(np.arange(r)), i32(before)
+        self.positions = i32(np.concatenate([np.arange(b, b + k) for b, k in zip(before, new)]))
+        self.slot_of_token = i32(np.concatenate([np.full(k, i) for i, k in enumerate(new)]))
+        self.max_new, self.max_context, self.attention_splits = max(new), max(total), None
+        self.heads, self.kv, self.d, self.dv = heads, kv, d, dv
+
+    def reference(self, scale, r1, r2):
+        out = np.zeros((self.n, self.heads, self.dv))
+        q = self.q.double().cpu().numpy().reshape(self.n, self.heads, self.d)
+        group, at = self.heads // self.kv, 0
+        for i in range(self.r):
+            k, v = self.k[i].double().numpy(), self.v[i].double().numpy()
+            for t in range(self.new[i]):
+                pos = self.before[i] + t
+                far = pos - np.arange(pos + 1)
+                for h in range(self.heads):
+                    s = k[:pos + 1, h // group] @ q[at, h] * scale - r1[h] * np.log(1.0 + r2[h] * far)
+                    w = np.exp(s - s.max())
+                    out[at, h] = (w / w.sum()) @ v[:pos + 1, h // group]
+                at += 1
+        return out.reshape(self.n, -1)
+
+
+@pytest.mark.parametrize("heads,kv,d,dv,page", [(4, 2, 16, 16, 16), (6, 2, 24, 8, 16), (3, 1, 40, 72, 32), (8, 8, 64, 64, 64),
+                                                (16, 2, 64, 128, 64), (2, 1, 136, 104, 16), (5, 5, 8, 200, 16)])
+@pytest.mark.parametrize("before,new", [([0, 3, 40, 129], [37, 1, 17, 2]), ([0, 63, 64, 700], [1, 1, 1, 1])])
+def test_distance_attention_on_the_tensor_cores(heads, kv, d, dv, page, before, new):
+    """Key and value sizes that differ and are not the tile's size; portions beside single tokens; decode steps with and
+    without their keys split among CTAs; the float32 kernel on the CUDA cores beside it."""
+    from hfee_b200.kernels import ops
+    rng = np.random.default_rng(heads + d)
+    r1, r2 = rng.uniform(0.2, 1.5, size=heads), rng.uniform(0.05, 2.0, size=heads)
+    scale, out_scale = 0.4 / np.sqrt(d), 0.7
+    assert ops.distance_attention_tile(d, dv) >= max(d, dv)
+    for dtype, tol in ((torch.bfloat16, 1.5e-2), (torch.float32, 2e-5)):
+        b = DistanceBatch(dtype, heads, kv, d, dv, page, before, new, seed=d)
+        want = b.reference(scale, r1, r2) * out_scale
+        tile = ops.distance_attention_tile(d, dv)
+        for splits in ((None, 3, 7) if max(new) == 1 and dtype == torch.bfloat16 else (None,)):
+            b.attention_splits = splits
+            scratch = torch.full((b.n * heads * (splits or 1) * (tile + 2),), float("nan"), dtype=torch.float32, device=DEV) if splits else None
+            out = torch.full((b.n, heads * dv), float("nan"), dtype=dtype, device=DEV)
+            ops.distance_attention(b.q, b.kp, b.vp, b.block_table, page, b, out, heads, kv, d, dv, scale, dev(r1), dev(r2), out_scale,
+                                   0, scratch)
+            assert close(out.float().cpu().numpy(), want, tol), (dtype, splits)
+
+
+def test_distance_penalty_decides_between_a_near_and_a_far_key():
+    """Two keys with the same score, one at distance 1 and one at distance 300: the weights follow (1 + r2 * distance)^-r1
+    alone, on both kernels."""
+    from hfee_b200.kernels import ops
+    heads, kv, d, dv, page, ctx = 2, 1, 16, 16, 16, 302
+    r1, r2 = np.array([1.0, 0.5]), np.array([0.5, 2.0])
+    for dtype, tol in ((torch.bfloat16, 1e-2), (torch.float32, 1e-5)):
+        b = DistanceBatch(dtype, heads, kv, d, dv, page, [ctx - 1], [1], seed=1)
+        k = torch.zeros(ctx, kv, d)
+        v = torch.zeros(ctx, kv, dv)
+        k[:, 0, 0] = -40.0                                  # every other key is out of the question
+        k[ctx - 2, 0, 0] = k[ctx - 1 - 300, 0, 0] = 0.0
+        k[ctx - 1, 0, 0] = -40.0
+        v[ctx - 2, 0, 0], v[ctx - 1 - 300, 0, 1] = 1.0, 1.0
+        for first in range(0, ctx, page):
+            pg, m = int(b.block_table[0, first // page]), min(page, ctx - first)
+            b.kp[pg, :, :m] = k[first:first + m].transpose(0, 1).to(dtype).to(DEV)
+            b.vp[pg, :, :m] = v[first:first + m].transpose(0, 1).to(dtype).to(DEV)
+        q = torch.zeros(1, heads * d)
+        q[0, 0] = q[0, d] = 1.0
+        out = torch.empty((1, heads * dv), dtype=dtype, device=DEV)
+        ops.distance_attention(q.to(dtype).to(DEV), b.kp, b.vp, b.block_table, page, b, out, heads, kv, d, dv, 1.0, dev(r1), dev(r2))
+        got = out.float().cpu().numpy().reshape(heads, dv)
+        for h in range(heads):
+            near, far = (1 + r2[h] * 1) ** -r1[h], (1 + r2[h] * 300) ** -r1[h]
+            assert abs(got[h, 0] - near / (near + far)) < tol and abs(got[h, 1] - far / (near + far)) < tol
+
+
+@pytest.mark.parametrize("n,experts,top,inner,width", [(1, 4, 2, 16, 32), (9, 3, 3, 24, 40), (300, 5, 2, 72, 64), (700, 2, 1, 136, 264)])
+def test_experts_on_the_tensor_cores(n, experts, top, inner, width):
+    """The grouped products over tiles of 128 places against a loop over tokens: experts with no token, with fewer than a
+    tile and with several tiles; NaN in the scratch rows that hold no pair."""
+    from hfee_b200.kernels import ops
+    rng = np.random.default_rng(n)
+    dtype, limit, alpha = torch.bfloat16, 0.8, 1.702
+    assert ops.moe_experts_grouped_ok(dtype, width, inner)
+    x = dev(rng.normal(size=(n, width)), dtype)
+    wgu = dev(rng.normal(size=(experts, 2 * inner, width)) * 0.2, dtype)
+    wd = dev(rng.normal(size=(experts, width, inner)) * 0.2, dtype)
+    logits = rng.normal(size=(n, experts))
+    if experts > top:
+        logits[:, experts - 1] = -50.0
+    choice = torch.empty((n, top), dtype=torch.int32, device=DEV)
+    weight = torch.empty((n, top), dtype=torch.float32, device=DEV)
+    ops.moe_route(dev(logits), top, 2.0, choice, weight)
+    tiles = ops.moe_tiles_grouped(n * top, experts)
+    rows = tiles * ops.GROUPED_TILE_ROWS
+    i32 = lambda k: torch.full((k,), 12345, dtype=torch.int32, device=DEV)
+    nan = lambda c, dt: torch.full((rows, c), float("nan"), dtype=dt, device=DEV)
+    place, row_pair, tile_group = i32(n * top), i32(rows), i32(tiles)
+    rows_out = nan(width, torch.float32)
+    ops.moe_experts_grouped(x, top, choice, wgu, wd, limit, place, row_pair, tile_group, nan(width, dtype), nan(2 * inner, dtype),
+                            nan(inner, dtype), rows_out, alpha)
+    ops.check_status()
+    pl, rp, tg, ch = place.cpu().numpy(), row_pair.cpu().numpy(), tile_group.cpu().numpy(), choice.cpu().numpy()
+    assert len(set(pl)) == n * top                                  # every pair has a row of its own, in a tile of its expert
+    for pair, row in enumerate(pl):
+        assert rp[row] == pair and tg[row // ops.GROUPED_TILE_ROWS] == ch[pair // top, pair % top]
+    f64 = lambda t: t.double().cpu().numpy()
+    X, GU, Dn, wt = f64(x), f64(wgu), f64(wd), f64(weight)
+    want = np.zeros((n, width))
+    for t in range(n):
+        for k in range(top):
+            e = ch[t, k]
+            g, u = np.minimum(GU[e, :inner] @ X[t], limit), np.clip(GU[e, inner:] @ X[t], -limit, limit)
+            want[t] += wt[t, k] * (Dn[e] @ (g / (1 + np.exp(-alpha * g)) * (u + 1)))
+    y0 = rng.normal(size=(n, width))
+    for accumulate in (False, True):
+        y = dev(y0)
+        ops.moe_combine(rows_out, weight, y, accumulate, place)
+        assert close(y.cpu().numpy(), want + (y0 if accumulate else 0.0), 2e-2)
