@@ -15,6 +15,11 @@ where that matters, and prints what it achieved against the roofline that bounds
     python -m hfee_b200.kernels.microbench latent_attention  --tokens 2048 --heads 32 --head-dim 64 --rank 256 --window 512 [--decode --batch 8]
     python -m hfee_b200.kernels.microbench head_linear       --tokens 2048 --heads 32 --head-dim 64 --rank 256
     python -m hfee_b200.kernels.microbench rope_norm_cache   --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64
+    python -m hfee_b200.kernels.microbench mingru            --tokens 2048 --channels 2048 [--decode --batch 8]
+    python -m hfee_b200.kernels.microbench selective_scan    --tokens 2048 --channels 2048 --state 16 [--decode --batch 8]
+    python -m hfee_b200.kernels.microbench distance_attention --tokens 2048 --heads 32 --kv-heads 8 --head-dim 64 [--value-dim 128] [--decode --batch 8]
+    python -m hfee_b200.kernels.microbench moe_experts       --tokens 2048 --k 2048 --inner 2048 --experts 16 --top 2
+    python -m hfee_b200.kernels.microbench row_ops           --tokens 2048 --k 2048 --inner 4096 --depth 6
 
 ``--iters`` timed launches follow ``--warmup`` untimed ones; ``--rotate`` distinct weight
 buffers are cycled so that a weight-streaming kernel never finds its weights in L2.  The
@@ -287,11 +292,122 @@ def _rope_norm_cache(args) -> dict:
     return {"kernel": "rope_norm_cache", "tokens": b.n, "us": round(sec * 1e6, 2), "gbs": round(2 * b.n * cols * 2 / sec / 1e9, 1)}
 
 
+def _mingru(args) -> dict:
+    """minGRU over ``--channels`` channels: one prompt portion, or a decode step of ``--batch`` requests."""
+    c = args.channels
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([0], [args.tokens])
+    b = _batch_of(before, new)
+    proj = torch.randn(b.n, 3 * c, device=DEV).to(torch.bfloat16)
+    zb, xb = torch.randn(c, device=DEV), torch.randn(c, device=DEV)
+    state = torch.zeros(b.r, c, device=DEV)
+    out = torch.empty(b.n, c, dtype=torch.bfloat16, device=DEV)
+    sec = _time(lambda i: ops.mingru(proj, 0, c, 2 * c, zb, xb, state, b, out, c, True), args.warmup, args.iters)
+    moved = b.n * 4 * c * 2 + 2 * b.r * c * 4
+    return {"kernel": "mingru", "channels": c, "requests": b.r, "tokens": b.n, "us": round(sec * 1e6, 2),
+            "gbs": round(moved / sec / 1e9, 1)}
+
+
+def _selective_scan(args) -> dict:
+    """Selective scan over ``--channels`` channels of ``--state`` entries: one prompt portion, or a decode step of ``--batch``."""
+    c, ns = args.channels, args.state
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([0], [args.tokens])
+    b = _batch_of(before, new)
+    xz = (torch.randn(b.n, 2 * c, device=DEV) * 0.5).to(torch.bfloat16)
+    bc = (torch.randn(b.n, 2 * ns, device=DEV) * 0.5).to(torch.bfloat16)
+    dt = torch.randn(b.n, c, device=DEV) - 2.0
+    a_log = torch.log(torch.arange(1, ns + 1, device=DEV, dtype=torch.float32)).repeat(c, 1).contiguous()
+    d_skip, dt_bias = torch.ones(c, device=DEV), torch.zeros(c, device=DEV)
+    state = torch.zeros(b.r, c, ns, device=DEV)
+    out = torch.empty(b.n, c, dtype=torch.bfloat16, device=DEV)
+    fn = lambda i: ops.selective_scan(xz[:, :c], dt, bc, 0, ns, xz[:, c:], a_log, d_skip, dt_bias, state, b, out, 1.0, True)
+    sec = _time(fn, args.warmup, args.iters)
+    moved = b.n * (3 * c * 2 + c * 4 + 2 * ns * 2) + 2 * b.r * c * ns * 4
+    return {"kernel": "selective_scan", "channels": c, "state": ns, "requests": b.r, "tokens": b.n, "us": round(sec * 1e6, 2),
+            "gbs": round(moved / sec / 1e9, 1), "exp_per_s_e12": round(b.n * c * ns / sec / 1e12, 3)}
+
+
+def _distance_attention(args) -> dict:
+    """Softmax attention with the logarithmic distance penalty: one prompt portion, or a decode step of ``--batch`` requests."""
+    heads, kv, hd, vd, page = args.heads, args.kv_heads, args.head_dim, args.value_dim or args.head_dim, args.page_size
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([args.context_before], [args.tokens])
+    b = _batch_of(before, new)
+    b.planning_context, b.attention_splits = b.max_context, args.splits or None
+    max_pages = -(-b.max_context // page)
+    table = torch.randperm(b.r * max_pages).reshape(b.r, max_pages).to(torch.int32).to(DEV)
+    kp = torch.randn(b.r * max_pages, kv, page, hd, device=DEV).to(torch.bfloat16)
+    vp = torch.randn(b.r * max_pages, kv, page, vd, device=DEV).to(torch.bfloat16)
+    q = torch.randn(b.n, heads * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty(b.n, heads * vd, dtype=torch.bfloat16, device=DEV)
+    r1, r2 = torch.linspace(0.5, 2.0, heads, device=DEV), torch.linspace(0.1, 1.0, heads, device=DEV)
+    tile = ops.distance_attention_tile(hd, vd)
+    scratch = torch.empty(b.r * heads * ops.MAX_SPLITS * (tile + 2), dtype=torch.float32, device=DEV) if args.decode and tile else None
+    fn = lambda i: ops.distance_attention(q, kp, vp, table, page, b, out, heads, kv, hd, vd, hd ** -0.5, r1, r2, 1.0, 0, scratch)
+    sec = _time(fn, args.warmup, args.iters)
+    total = [s + c for s, c in zip(before, new)]
+    kv_bytes = sum(total) * kv * (hd + vd) * 2
+    flops = sum(2.0 * heads * (hd + vd) * (c * s + c * (c + 1) / 2) for s, c in zip(before, new))
+    return {"kernel": "distance_attention", "heads": heads, "kv_heads": kv, "head_dim": hd, "value_dim": vd, "requests": b.r,
+            "context": b.max_context, "us": round(sec * 1e6, 2), "kv_gbs": round(kv_bytes / sec / 1e9, 1),
+            "tflops": round(flops / sec / 1e12, 1)}
+
+
+def _moe_experts(args) -> dict:
+    """The routed experts of ``--tokens`` tokens (``--experts`` of inner size ``--inner``, ``--top`` a token, width ``--k``):
+    plan, gather, both grouped products and the activation between them, and the weighted sum."""
+    n, w, f, e, top = args.tokens, args.k, args.inner, args.experts, args.top
+    x = torch.randn(n, w, device=DEV).to(torch.bfloat16)
+    w_gu = (torch.randn(e, 2 * f, w, device=DEV) * w ** -0.5).to(torch.bfloat16)
+    w_d = (torch.randn(e, w, f, device=DEV) * f ** -0.5).to(torch.bfloat16)
+    logits = torch.randn(n, e, device=DEV)
+    choice = torch.empty(n, top, dtype=torch.int32, device=DEV)
+    weight = torch.empty(n, top, dtype=torch.float32, device=DEV)
+    ops.moe_route(logits, top, 1.0, choice, weight)
+    tiles = ops.moe_tiles_grouped(n * top, e)
+    rows = tiles * ops.GROUPED_TILE_ROWS
+    i32 = lambda k: torch.empty(k, dtype=torch.int32, device=DEV)
+    place, row_pair, tile_group = i32(n * top), i32(rows), i32(tiles)
+    bf = lambda c: torch.empty(rows, c, dtype=torch.bfloat16, device=DEV)
+    rows_in, gate_up, hidden = bf(w), bf(2 * f), bf(f)
+    rows_out = torch.empty(rows, w, dtype=torch.float32, device=DEV)
+    y = torch.zeros(n, w, dtype=torch.float32, device=DEV)
+
+    def fn(i):
+        ops.moe_experts_grouped(x, top, choice, w_gu, w_d, 7.0, place, row_pair, tile_group, rows_in, gate_up, hidden, rows_out)
+        ops.moe_combine(rows_out, weight, y, False, place)
+    sec = _time(fn, args.warmup, args.iters)
+    flops = 2.0 * n * top * 3 * f * w
+    return {"kernel": "moe_experts_grouped", "tokens": n, "width": w, "inner": f, "experts": e, "top": top, "tiles": tiles,
+            "us": round(sec * 1e6, 2), "tflops": round(flops / sec / 1e12, 1)}
+
+
+def _row_ops(args) -> dict:
+    """The row kernels of the scaled pre-norm block with a depth average, the clamped gated activation and the sinusoid, on
+    ``--tokens`` rows of width ``--k`` (activation: inner size ``--inner``): microseconds and GB/s each."""
+    n, w, f, depth = args.tokens, args.k, args.inner, args.depth
+    res = {"kernel": "row_ops", "tokens": n, "width": w}
+    x, y = torch.randn(n, w, device=DEV), torch.randn(n, w, device=DEV)
+    hist = torch.randn(depth + 1, n, w, device=DEV)
+    wts = torch.full((depth + 1,), 1.0 / (depth + 1), device=DEV)
+    sec = _time(lambda i: ops.depth_average(x, y, 0.5, hist, wts, depth - 1), args.warmup, args.iters)
+    res["depth_average"] = {"entries": depth + 1, "us": round(sec * 1e6, 2), "gbs": round(n * w * 4 * (depth + 4) / sec / 1e9, 1)}
+    nw, out = torch.ones(w, device=DEV), torch.empty(n, w, dtype=torch.bfloat16, device=DEV)
+    sec = _time(lambda i: ops.scaled_add_norm(y, 0.5, x, nw, 1e-5, out), args.warmup, args.iters)
+    res["scaled_add_norm"] = {"us": round(sec * 1e6, 2), "gbs": round(n * w * 14 / sec / 1e9, 1)}
+    gu, h = torch.randn(n, 2 * f, device=DEV).to(torch.bfloat16), torch.empty(n, f, dtype=torch.bfloat16, device=DEV)
+    sec = _time(lambda i: ops.clamped_glu(gu, h, 7.0), args.warmup, args.iters)
+    res["clamped_glu"] = {"inner": f, "us": round(sec * 1e6, 2), "gbs": round(n * f * 6 / sec / 1e9, 1)}
+    pos = torch.arange(n, dtype=torch.int32, device=DEV)
+    sec = _time(lambda i: ops.add_sinusoid(x, pos), args.warmup, args.iters)
+    res["add_sinusoid"] = {"us": round(sec * 1e6, 2), "gbs": round(n * w * 8 / sec / 1e9, 1)}
+    return res
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["delta_rule", "conv_act", "latent_attention", "head_linear", "rope_norm_cache",
                                        "gemm_tcgen05", "gemm_stream", "gemm_skinny", "gemm_ring", "gemm_pair", "attention_decode", "attention_prefill",
-                                      "sigmoid_attention", "linear_attention"])
+                                      "sigmoid_attention", "linear_attention", "mingru", "selective_scan",
+                                       "distance_attention", "moe_experts", "row_ops"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -311,6 +427,13 @@ def main(argv=None) -> int:
     ap.add_argument("--window", type=int, default=512, help="latent_attention: sliding window (0: all earlier positions)")
     ap.add_argument("--chunk", type=int, default=128, help="sigmoid_attention: positions per block of the mask")
     ap.add_argument("--decode", action="store_true", help="sigmoid_attention / linear_attention: a decode step of --batch requests")
+    ap.add_argument("--channels", type=int, default=2048, help="mingru / selective_scan: channels of the recurrence")
+    ap.add_argument("--state", type=int, default=16, help="selective_scan: state entries per channel")
+    ap.add_argument("--value-dim", type=int, default=0, help="distance_attention: value size per head (0: the key size)")
+    ap.add_argument("--experts", type=int, default=16)
+    ap.add_argument("--top", type=int, default=2)
+    ap.add_argument("--inner", type=int, default=2048, help="moe_experts / row_ops: inner size of an expert")
+    ap.add_argument("--depth", type=int, default=6, help="row_ops: layers in front of the depth average")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tc-attention", action="store_true", help="attention_prefill: the tcgen05 kernel (the default)")
@@ -330,6 +453,9 @@ def main(argv=None) -> int:
     elif args.kernel in ("delta_rule", "conv_act", "latent_attention", "head_linear", "rope_norm_cache"):
         res = {"delta_rule": _delta_rule, "conv_act": _conv_act, "latent_attention": _latent_attention,
                "head_linear": _head_linear, "rope_norm_cache": _rope_norm_cache}[args.kernel](args)
+    elif args.kernel in ("mingru", "selective_scan", "distance_attention", "moe_experts", "row_ops"):
+        res = {"mingru": _mingru, "selective_scan": _selective_scan, "distance_attention": _distance_attention,
+               "moe_experts": _moe_experts, "row_ops": _row_ops}[args.kernel](args)
     else:
         res = _attention(args, args.kernel == "attention_decode")
     print(json.dumps(res))

@@ -1683,6 +1683,8 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, slots
 for _name in ("rmsnorm_add_norm", "latent_attention", "linear_act", "attention_simt_general", "rope_norm_cache", "latent_norm_rope_cache", "head_linear", "conv_act", "delta_rule",
               "head_norm_gate", "unary_act", "head_gate", "attention_simt_masked", "short_conv", "linear_attention", "rmsnorm_add", "norm_gate", "gated_act", "scale_", "cast_rows", "sigmoid_attention",
               "qk_norm_rope_cache", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu", "linear_rope_cache",
-              "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain"):
+              "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain",
+              "mingru", "selective_scan", "distance_attention", "moe_route", "moe_plan", "moe_experts", "moe_experts_grouped", "moe_combine",
+              "clamped_glu", "depth_average", "scaled_add_norm", "scaled_add", "add_sinusoid", "softcap_"):
     globals()[_name] = _measurable(globals()[_name])
 del _name
