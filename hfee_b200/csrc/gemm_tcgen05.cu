@@ -41,7 +41,7 @@ constexpr int EPI_WARPS = 8;
 constexpr int ACC_STAGES = 2;
 constexpr int SK_MAX_PIECES = 4;      // a tile is cut into at most this many ranges of K blocks
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4, EPI_RELU2 = 5 };   // 5: store relu(x)^2
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4, EPI_RELU2 = 5, EPI_CLAMPED = 6 };   // 5: store relu(x)^2; 6: the clamped gated activation
 
 template <int BN> struct TileCfg {
   static constexpr int STAGES = BN == 128 ? 6 : 4;
@@ -285,7 +285,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
         }
         if (row >= M || col0 >= N) continue;
-        if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
+        if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU || EPI == EPI_CLAMPED) {
           // columns in groups of 8 = [4 gate | 4 up] -> 4 outputs per group at column col/2
           TOut* dst = C + (long long)row * ldc + col0 / 2;
           float o[16];
@@ -294,7 +294,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               float gate = __uint_as_float(v[gq * 8 + i]), up = __uint_as_float(v[gq * 8 + 4 + i]);
-              o[gq * 4 + i] = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
+              if constexpr (EPI == EPI_CLAMPED) {
+                gate = fminf(gate, rope.act_limit);
+                up = fminf(fmaxf(up, -rope.act_limit), rope.act_limit);
+                o[gq * 4 + i] = __fdividef(gate, 1.f + __expf(-rope.act_alpha * gate)) * (up + 1.f);
+              } else {
+                o[gq * 4 + i] = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
+              }
             }
           if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -513,14 +519,14 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
 // Grouped product: A [M, K] holds rows in tiles of 128 (M a multiple of 128), W [groups * N, K] one [N, K] matrix per
 // group stacked by rows; C[tile i's rows] = A[tile i's rows] . W[tile_group[i]]^T, tiles with a negative group are
 // left alone.  tile_group (device, M / 128 ints) is read by the kernel, so the launch does not depend on it.
-// C: bfloat16 or float32 [M, ldc], stored.
+// C: bfloat16 or float32 [M, ldc], stored; with `clamped` the clamped gated activation of the product (limit, alpha) instead.
 HFEE_API int hfee_gemm_tcgen05_grouped(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
-                                       int out_dtype, int M, int N, int K, int groups, const int* tile_group, int* status,
-                                       cudaStream_t stream) {
+                                       int out_dtype, int M, int N, int K, int groups, const int* tile_group, int clamped,
+                                       float limit, float alpha, int* status, cudaStream_t stream) {
   if (M == 0 || N == 0) return HFEE_OK;
   HFEE_REQUIRE(M > 0 && M % BM == 0 && N > 0 && K > 0 && K % 8 == 0 && groups > 0 && tile_group != nullptr,
                "gemm_tcgen05_grouped: M=%d must be a multiple of 128 and K=%d a multiple of 8", M, K);
-  HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K && ldc >= N,
+  HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K && ldc >= (clamped ? N / 2 : N),
                "gemm_tcgen05_grouped: leading dimensions (%lld, %lld) must be multiples of 8 and at least K", lda, ldw);
   HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05_grouped: operands must be 16-byte aligned");
   HFEE_REQUIRE((long long)groups * N < (1ll << 31), "gemm_tcgen05_grouped: too many rows of W");
@@ -532,6 +538,15 @@ HFEE_API int hfee_gemm_tcgen05_grouped(const void* A, long long lda, const void*
   if (rc != HFEE_OK) return rc;
   rc = make_map(&mw, W, (long long)groups * N, K, ldw, bn);
   if (rc != HFEE_OK) return rc;
+  if (clamped) {       // every group's rows in groups of [4 gate | 4 up]; C [M, N/2] bfloat16 holds the clamped gated activation
+    HFEE_REQUIRE(out_dtype == HFEE_BF16 && N % 8 == 0, "gemm_tcgen05_grouped: the gated epilogue writes bfloat16 and needs N %% 8 == 0, got %d", N);
+    RopeEpi par = RopeEpi{};
+    par.act_limit = limit;
+    par.act_alpha = alpha;
+    if (bn == 256) return launch<256, EPI_CLAMPED, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, par, tile_group, N);
+    return launch<128, EPI_CLAMPED, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, par, tile_group, N);
+  }
+  HFEE_REQUIRE(ldc >= N, "gemm_tcgen05_grouped: ldc=%lld is too small", ldc);
   if (bn == 256) {
     if (out_dtype == HFEE_BF16)
       return launch<256, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, RopeEpi{}, tile_group, N);

@@ -40,7 +40,7 @@ template <int BN> struct PairCfg {
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;
 };
 
-enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4, EPI_RELU2 = 5 };   // 5: store relu(x)^2
+enum Epilogue { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_ROPE = 3, EPI_GEGLU = 4, EPI_RELU2 = 5, EPI_CLAMPED = 6 };   // 5: store relu(x)^2; 6: the clamped gated activation
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -224,7 +224,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
         }
         if (row >= M || col0 >= N) continue;
-        if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU) {
+        if constexpr (EPI == EPI_SWIGLU || EPI == EPI_GEGLU || EPI == EPI_CLAMPED) {
           // columns in groups of 8 = [4 gate | 4 up] -> 4 outputs per group at column col / 2
           TOut* dst = C + (long long)row * ldc + col0 / 2;
           float o[16];
@@ -233,7 +233,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               float gate = __uint_as_float(v[gq * 8 + i]), up = __uint_as_float(v[gq * 8 + 4 + i]);
-              o[gq * 4 + i] = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
+              if constexpr (EPI == EPI_CLAMPED) {
+                gate = fminf(gate, rope.act_limit);
+                up = fminf(fmaxf(up, -rope.act_limit), rope.act_limit);
+                o[gq * 4 + i] = __fdividef(gate, 1.f + __expf(-rope.act_alpha * gate)) * (up + 1.f);
+              } else {
+                o[gq * 4 + i] = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
+              }
             }
           if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -412,6 +418,26 @@ HFEE_API int hfee_gemm_tcgen05_pair(const void* A, long long lda, const void* W,
   }
   if (out_dtype == HFEE_BF16) return launch_pair<256, EPI_STORE, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream);
   return launch_pair<256, EPI_STORE, float>(ma, mw, C, ldc, M, N, K, status, stream);
+}
+
+// The gate/up product of a clamped gated feed-forward: W rows in groups of [4 gate | 4 up], C [M, N/2] bfloat16 =
+// g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), applied to the float32 accumulator.
+HFEE_API int hfee_gemm_tcgen05_pair_clamped(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
+                                            int M, int N, int K, float limit, float alpha, int* status, cudaStream_t stream) {
+  if (M == 0 || N == 0) return HFEE_OK;
+  HFEE_REQUIRE(M > 0 && N > 0 && N % 8 == 0 && K > 0 && K % 8 == 0, "gemm_tcgen05_pair_clamped: N=%d and K=%d must be positive multiples of 8", N, K);
+  HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K && ldc >= N / 2,
+               "gemm_tcgen05_pair_clamped: leading dimensions (%lld, %lld, %lld) do not fit", lda, ldw, ldc);
+  HFEE_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05_pair_clamped: operands must be 16-byte aligned");
+  CUtensorMap ma, mw;
+  int rc = make_map(&ma, A, M, K, lda, BM);
+  if (rc != HFEE_OK) return rc;
+  rc = make_map(&mw, W, N, K, ldw, 128);
+  if (rc != HFEE_OK) return rc;
+  RopeEpi par = RopeEpi{};
+  par.act_limit = limit;
+  par.act_alpha = alpha;
+  return launch_pair<256, EPI_CLAMPED, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream, par);
 }
 
 // The q/k/v product with rotation and cache write in its epilogue (hfee_gemm_tcgen05_rope) on pairs of

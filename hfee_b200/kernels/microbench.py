@@ -356,7 +356,7 @@ def _moe_experts(args) -> dict:
     plan, gather, both grouped products and the activation between them, and the weighted sum."""
     n, w, f, e, top = args.tokens, args.k, args.inner, args.experts, args.top
     x = torch.randn(n, w, device=DEV).to(torch.bfloat16)
-    w_gu = (torch.randn(e, 2 * f, w, device=DEV) * w ** -0.5).to(torch.bfloat16)
+    w_gu = (torch.randn(e, 2 * f, w, device=DEV) * w ** -0.5).to(torch.bfloat16)      # rows in runs of [4 gate | 4 up]
     w_d = (torch.randn(e, w, f, device=DEV) * f ** -0.5).to(torch.bfloat16)
     logits = torch.randn(n, e, device=DEV)
     choice = torch.empty(n, top, dtype=torch.int32, device=DEV)
@@ -367,7 +367,7 @@ def _moe_experts(args) -> dict:
     i32 = lambda k: torch.empty(k, dtype=torch.int32, device=DEV)
     place, row_pair, tile_group = i32(n * top), i32(rows), i32(tiles)
     bf = lambda c: torch.empty(rows, c, dtype=torch.bfloat16, device=DEV)
-    rows_in, gate_up, hidden = bf(w), bf(2 * f), bf(f)
+    rows_in, gate_up, hidden = bf(w), (bf(2 * f) if args.unfused else None), bf(f)
     rows_out = torch.empty(rows, w, dtype=torch.float32, device=DEV)
     y = torch.zeros(n, w, dtype=torch.float32, device=DEV)
 
@@ -433,6 +433,7 @@ def main(argv=None) -> int:
     ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--top", type=int, default=2)
     ap.add_argument("--inner", type=int, default=2048, help="moe_experts / row_ops: inner size of an expert")
+    ap.add_argument("--unfused", action="store_true", help="moe_experts: the activation as a pass of its own")
     ap.add_argument("--depth", type=int, default=6, help="row_ops: layers in front of the depth average")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--iters", type=int, default=20)

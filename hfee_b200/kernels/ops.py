@@ -89,7 +89,8 @@ _SIGNATURES = {
     "hfee_moe_combine": [_P, _P, _P, _I, _I, _P, _I, _I, _P],
     "hfee_moe_plan_tiles": [_P, _I, _I, _I, _P, _P, _P, _I, _P],
     "hfee_moe_gather_rows": [_P, _L, _I, _P, _P, _I, _P, _L, _I, _I, _P],
-    "hfee_gemm_tcgen05_grouped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _P, _P],
+    "hfee_gemm_tcgen05_grouped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _I, _F, _F, _P, _P],
+    "hfee_gemm_tcgen05_pair_clamped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _F, _F, _P, _P],
     "hfee_conv_act_launches": [_I, _I, _I],
     "hfee_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P],
     "hfee_head_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
@@ -1531,18 +1532,54 @@ def moe_experts_grouped_ok(x_dtype: torch.dtype, width: int, inner: int) -> bool
     return x_dtype == torch.bfloat16 and width % 8 == 0 and inner % 8 == 0
 
 
-def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor) -> None:
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor,
+                         clamped: Optional[tuple] = None) -> None:
     """out[rows of tile i] = a[rows of tile i] @ w[tile_group[i]].T for tiles of GROUPED_TILE_ROWS rows; tiles whose
     group is negative are left alone.  ``a`` [tiles * 128, k] bfloat16, ``w`` [groups, n, k] bfloat16 contiguous,
-    ``out`` [tiles * 128, n] bfloat16 or float32.  ``tile_group`` is read on the device."""
+    ``out`` [tiles * 128, n] bfloat16 or float32.  ``tile_group`` is read on the device.  With ``clamped`` = (limit,
+    alpha) every group's rows come in runs of [4 gate | 4 up] and ``out`` [tiles * 128, n / 2] bfloat16 receives
+    :func:`clamped_glu` of the product, applied to the float32 accumulator."""
     lib = library()
     m, k = a.shape
     groups, n = w.shape[0], w.shape[1]
     _i32(tile_group, "tile_group")
     assert w.shape[2] == k and w.is_contiguous() and a.dtype == w.dtype == torch.bfloat16
-    assert m % GROUPED_TILE_ROWS == 0 and tile_group.numel() >= m // GROUPED_TILE_ROWS and tuple(out.shape) == (m, n)
+    assert m % GROUPED_TILE_ROWS == 0 and tile_group.numel() >= m // GROUPED_TILE_ROWS
+    assert tuple(out.shape) == (m, n // 2 if clamped else n)
+    limit, alpha = clamped or (0.0, 0.0)
     _check(lib.hfee_gemm_tcgen05_grouped(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), k, out.data_ptr(), _rows(out, "gemm out"),
-                                         _dt(out), m, n, k, groups, tile_group.data_ptr(), _status().data_ptr(), _stream()), lib)
+                                         _dt(out), m, n, k, groups, tile_group.data_ptr(), int(clamped is not None), float(limit),
+                                         float(alpha), _status().data_ptr(), _stream()), lib)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, granule: int = 4) -> torch.Tensor:
+    """[..., inner, k] twice -> [..., 2 * inner, k] with the rows in runs of ``granule`` gate rows and ``granule`` up rows,
+    the layout of the gated epilogues."""
+    inner = gate.shape[-2]
+    lead = gate.shape[:-2]
+    w = torch.stack([gate.reshape(*lead, inner // granule, granule, -1), up.reshape(*lead, inner // granule, granule, -1)], dim=-3)
+    return w.reshape(*lead, 2 * inner, -1).contiguous()
+
+
+CLAMPED_PAIR_MIN_TOKENS = 65
+
+
+def linear_clamped_glu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, granule: int, scratch: torch.Tensor,
+                       limit: float, alpha: float = 1.702) -> None:
+    """out = :func:`clamped_glu` of ``a @ w_gate_up^T`` (rows of ``w_gate_up`` in runs of ``granule`` gate and ``granule`` up
+    rows): in the epilogue of the paired tcgen05 product for prompt portions in bfloat16, else through ``scratch``
+    [m, 2 * inner]."""
+    m, k = a.shape
+    n = w_gate_up.shape[0]
+    if (granule == SWIGLU_GRANULE and n % 8 == 0 and m >= CLAMPED_PAIR_MIN_TOKENS and USE_TCGEN05 and USE_PAIRS
+            and _tensor_core_ok(a, w_gate_up) and out.dtype == torch.bfloat16):
+        lib = library()
+        _check(lib.hfee_gemm_tcgen05_pair_clamped(a.data_ptr(), _rows(a, "gemm a"), w_gate_up.data_ptr(), _rows(w_gate_up, "gemm w"),
+                                                  out.data_ptr(), _rows(out, "gemm out"), m, n, k, float(limit), float(alpha),
+                                                  _status().data_ptr(), _stream()), lib)
+        return
+    linear(a, w_gate_up, scratch)
+    clamped_glu(scratch, out, limit, alpha, granule)
 
 
 def moe_experts_grouped(x: torch.Tensor, top: int, choice: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float,
@@ -1553,7 +1590,9 @@ def moe_experts_grouped(x: torch.Tensor, top: int, choice: torch.Tensor, w_gate_
     (token, chosen expert e) pair, float32.  ``w_gate_up`` [experts, 2 * inner, width] holds each expert's gate rows, then
     its up rows; ``w_down`` [experts, width, inner].  Scratch, all of ``tiles * 128`` rows with ``tiles =
     moe_tiles_grouped(pairs, experts)``: ``rows_in`` [., width], ``gate_up`` [., 2 * inner], ``hidden`` [., inner]
-    (bfloat16), ``rows_out`` [., width] float32; ``place`` [pairs], ``row_pair`` [tiles * 128], ``tile_group`` [tiles]."""
+    (bfloat16), ``rows_out`` [., width] float32; ``place`` [pairs], ``row_pair`` [tiles * 128], ``tile_group`` [tiles].
+    With ``gate_up`` None each expert's rows of ``w_gate_up`` come in runs of [4 gate | 4 up] (:func:`interleave_gate_up`)
+    and the activation runs in the first product's epilogue."""
     lib = library()
     n, width = x.shape
     experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // 2
@@ -1563,13 +1602,16 @@ def moe_experts_grouped(x: torch.Tensor, top: int, choice: torch.Tensor, w_gate_
     for t in (choice, place, row_pair, tile_group):
         _i32(t, "moe plan")
     assert choice.numel() == pairs and place.numel() >= pairs and row_pair.numel() >= rows and tile_group.numel() >= tiles
-    assert rows_in.shape[0] >= rows and gate_up.shape[0] >= rows and hidden.shape[0] >= rows and rows_out.shape[0] >= rows
+    assert rows_in.shape[0] >= rows and (gate_up is None or gate_up.shape[0] >= rows) and hidden.shape[0] >= rows and rows_out.shape[0] >= rows
     _check(lib.hfee_moe_plan_tiles(choice.data_ptr(), pairs, experts, GROUPED_TILE_ROWS, place.data_ptr(), row_pair.data_ptr(),
                                    tile_group.data_ptr(), tiles, _stream()), lib)
     _check(lib.hfee_moe_gather_rows(x.data_ptr(), _rows(x, "x"), top, row_pair.data_ptr(), tile_group.data_ptr(), GROUPED_TILE_ROWS,
                                     rows_in.data_ptr(), _rows(rows_in, "rows_in"), width, tiles, _stream()), lib)
-    gemm_tcgen05_grouped(rows_in[:rows], w_gate_up, tile_group, gate_up[:rows])
-    clamped_glu(gate_up[:rows], hidden[:rows], limit, alpha)
+    if gate_up is None:         # the activation in the first product's epilogue
+        gemm_tcgen05_grouped(rows_in[:rows], w_gate_up, tile_group, hidden[:rows], clamped=(limit, alpha))
+    else:
+        gemm_tcgen05_grouped(rows_in[:rows], w_gate_up, tile_group, gate_up[:rows])
+        clamped_glu(gate_up[:rows], hidden[:rows], limit, alpha)
     gemm_tcgen05_grouped(hidden[:rows], w_down, tile_group, rows_out[:rows])
 
 
@@ -1685,6 +1727,6 @@ for _name in ("rmsnorm_add_norm", "latent_attention", "linear_act", "attention_s
               "qk_norm_rope_cache", "embed", "rmsnorm", "rope_table", "rope_cache_write", "swiglu", "linear", "linear_normed", "linear_swiglu", "linear_rope_cache",
               "linear_swiglu_normed", "paged_attention", "paged_attention_rope", "sample", "argmax", "sample_chain",
               "mingru", "selective_scan", "distance_attention", "moe_route", "moe_plan", "moe_experts", "moe_experts_grouped", "moe_combine",
-              "clamped_glu", "depth_average", "scaled_add_norm", "scaled_add", "add_sinusoid", "softcap_"):
+              "clamped_glu", "linear_clamped_glu", "depth_average", "scaled_add_norm", "scaled_add", "add_sinusoid", "softcap_"):
     globals()[_name] = _measurable(globals()[_name])
 del _name

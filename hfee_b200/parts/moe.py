@@ -8,7 +8,9 @@ The chosen weights are not renormalised.  The experts' tensors are stacked at lo
 each expert's gate rows and then its up rows, and ``[experts, width, inner]``); the (token, choice) pairs are ordered by
 expert on the device, so the launches of a step depend on its token count alone and the step replays from a CUDA graph.
 In bfloat16 with rows of whole 16-byte pieces the two products run on the tensor cores as grouped products over tiles of
-128 places that never span two experts; otherwise (float32) on the CUDA cores in tiles of 32 places.
+128 places that never span two experts, the activation in the first one's epilogue (gate and up rows stored in runs of
+four); otherwise (float32) on the CUDA cores in tiles of 32 places.  The shared expert's activation runs in the epilogue
+of its gate/up product for prompt portions in bfloat16.
 """
 from __future__ import annotations
 
@@ -51,18 +53,30 @@ class RoutedExperts(Part):
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"top {self.top} is outside 1..{self.experts}")
         self.w_router = tensors["router"]
-        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
-                                      for e in range(self.experts)]).contiguous()
-        self.w_gate, self.w_up = self.w_gate_up[:, :self.inner], self.w_gate_up[:, self.inner:]
+        pairs = rt.max_tokens * self.top
+        self.grouped = ops.moe_experts_grouped_ok(rt.dtype, self.width, self.inner)
+        self.tiles = ops.moe_tiles_grouped(pairs, self.experts) if self.grouped else ops.moe_max_tiles(pairs, self.experts)
+        g = ops.SWIGLU_GRANULE
+        gates = torch.stack([tensors[f"e{e}.gate"] for e in range(self.experts)])
+        ups = torch.stack([tensors[f"e{e}.up"] for e in range(self.experts)])
+        # grouped products: gate and up rows in runs of four, so that the first product's epilogue applies the activation
+        self.fused_act = self.grouped and self.inner % g == 0
+        if self.fused_act:
+            self.w_gate_up = ops.interleave_gate_up(gates, ups, g)
+        else:
+            self.w_gate_up = torch.cat([gates, ups], dim=1).contiguous()
+            self.w_gate, self.w_up = self.w_gate_up[:, :self.inner], self.w_gate_up[:, self.inner:]
+        del gates, ups
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
         self.shared_inner = spec.get("shared_inner")
         if self.shared_inner is not None:
             self.shared_inner, self.shared_limit = int(self.shared_inner), float(spec.shared_limit)
-            self.w_shared_in = torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0).contiguous()
+            gate, up = tensors["shared.gate"], tensors["shared.up"]
+            if gate.dtype == torch.bfloat16 and self.shared_inner % g == 0:
+                self.shared_granule, self.w_shared_in = g, ops.interleave_gate_up(gate, up, g)
+            else:
+                self.shared_granule, self.w_shared_in = self.shared_inner, torch.cat([gate, up], dim=0).contiguous()
             self.w_shared_down = tensors["shared.down"]
-        pairs = rt.max_tokens * self.top
-        self.grouped = ops.moe_experts_grouped_ok(rt.dtype, self.width, self.inner)
-        self.tiles = ops.moe_tiles_grouped(pairs, self.experts) if self.grouped else ops.moe_max_tiles(pairs, self.experts)
 
     def forward(self, xn, out: torch.Tensor, step: Any, accumulate: bool = True) -> None:
         n, rt, top = step.n, self.rt, self.top
@@ -81,7 +95,7 @@ class RoutedExperts(Part):
             row_pair = rt.scratch("moe_row_pair", (rows,), i32)
             tile_group = rt.scratch("moe_tile_group", (self.tiles,), i32)
             rows_in = rt.scratch("moe_rows_in", (rows, self.width))
-            gate_up = rt.scratch("moe_gate_up", (rows, 2 * self.inner))
+            gate_up = None if self.fused_act else rt.scratch("moe_gate_up", (rows, 2 * self.inner))
             hidden = rt.scratch("moe_hidden_rows", (rows, self.inner))
             pair_out = rt.scratch("moe_rows_out", (rows, self.width), torch.float32)
             ops.tag("experts")
@@ -103,8 +117,7 @@ class RoutedExperts(Part):
             gu = rt.scratch("ffn_gate_up", (rt.max_tokens, pad8(2 * s)))[:n, :2 * s]
             h = rt.scratch("ffn_hidden", (rt.max_tokens, pad8(s)))[:n, :s]
             ops.tag("gate_up")
-            ops.linear(xn, self.w_shared_in, gu)
-            ops.clamped_glu(gu, h, self.shared_limit, self.alpha)
+            ops.linear_clamped_glu(xn, self.w_shared_in, h, self.shared_granule, gu, self.shared_limit, self.alpha)
             ops.tag("down")
             ops.linear(h, self.w_shared_down, out, accumulate=accumulate)
             accumulate = True

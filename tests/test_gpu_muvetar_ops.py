@@ -346,10 +346,12 @@ def test_distance_penalty_decides_between_a_near_and_a_far_key():
             assert abs(got[h, 0] - near / (near + far)) < tol and abs(got[h, 1] - far / (near + far)) < tol
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("n,experts,top,inner,width", [(1, 4, 2, 16, 32), (9, 3, 3, 24, 40), (300, 5, 2, 72, 64), (700, 2, 1, 136, 264)])
-def test_experts_on_the_tensor_cores(n, experts, top, inner, width):
+def test_experts_on_the_tensor_cores(n, experts, top, inner, width, fused):
     """The grouped products over tiles of 128 places against a loop over tokens: experts with no token, with fewer than a
-    tile and with several tiles; NaN in the scratch rows that hold no pair."""
+    tile and with several tiles; NaN in the scratch rows that hold no pair.  ``fused``: gate and up rows in runs of four
+    and the activation in the first product's epilogue."""
     from hfee_b200.kernels import ops
     rng = np.random.default_rng(n)
     dtype, limit, alpha = torch.bfloat16, 0.8, 1.702
@@ -369,8 +371,12 @@ def test_experts_on_the_tensor_cores(n, experts, top, inner, width):
     nan = lambda c, dt: torch.full((rows, c), float("nan"), dtype=dt, device=DEV)
     place, row_pair, tile_group = i32(n * top), i32(rows), i32(tiles)
     rows_out = nan(width, torch.float32)
-    ops.moe_experts_grouped(x, top, choice, wgu, wd, limit, place, row_pair, tile_group, nan(width, dtype), nan(2 * inner, dtype),
-                            nan(inner, dtype), rows_out, alpha)
+    if fused:
+        ops.moe_experts_grouped(x, top, choice, ops.interleave_gate_up(wgu[:, :inner], wgu[:, inner:]), wd, limit, place, row_pair,
+                                tile_group, nan(width, dtype), None, nan(inner, dtype), rows_out, alpha)
+    else:
+        ops.moe_experts_grouped(x, top, choice, wgu, wd, limit, place, row_pair, tile_group, nan(width, dtype), nan(2 * inner, dtype),
+                                nan(inner, dtype), rows_out, alpha)
     ops.check_status()
     pl, rp, tg, ch = place.cpu().numpy(), row_pair.cpu().numpy(), tile_group.cpu().numpy(), choice.cpu().numpy()
     assert len(set(pl)) == n * top                                  # every pair has a row of its own, in a tile of its expert
@@ -389,3 +395,23 @@ def test_experts_on_the_tensor_cores(n, experts, top, inner, width):
         y = dev(y0)
         ops.moe_combine(rows_out, weight, y, accumulate, place)
         assert close(y.cpu().numpy(), want + (y0 if accumulate else 0.0), 2e-2)
+
+
+@pytest.mark.parametrize("n,inner,width,limit", [(65, 8, 16, 0.5), (200, 72, 64, 0.8), (300, 520, 264, 7.0), (2, 24, 40, 0.8)])
+def test_gate_up_product_with_the_clamped_activation(n, inner, width, limit):
+    """The gate/up product whose epilogue applies the clamped gated activation (prompt portions) and its route through
+    a buffer (few tokens), against float64; the limit is low enough to cut some gates and ups."""
+    from hfee_b200.kernels import ops
+    rng = np.random.default_rng(inner)
+    dtype, alpha = torch.bfloat16, 1.702
+    x = dev(rng.normal(size=(n, width)), dtype)
+    wg, wu = dev(rng.normal(size=(inner, width)) * 0.3, dtype), dev(rng.normal(size=(inner, width)) * 0.3, dtype)
+    out = torch.full((n, inner), float("nan"), dtype=dtype, device=DEV)
+    scratch = torch.empty((n, 2 * inner), dtype=dtype, device=DEV)
+    ops.linear_clamped_glu(x, ops.interleave_gate_up(wg, wu), out, ops.SWIGLU_GRANULE, scratch, limit, alpha)
+    ops.check_status()
+    X = x.double().cpu().numpy()
+    g = np.minimum(X @ wg.double().cpu().numpy().T, limit)
+    u = np.clip(X @ wu.double().cpu().numpy().T, -limit, limit)
+    assert (g == limit).any() and (np.abs(u) == limit).any()
+    assert close(out.float().cpu().numpy(), g / (1 + np.exp(-alpha * g)) * (u + 1), 2e-2)
