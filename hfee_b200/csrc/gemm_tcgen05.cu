@@ -74,8 +74,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   unsigned char* epi_stage = tiles + STAGES * Cfg::STAGE_BYTES;      // 1024-aligned: the tiles are whole KBs
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_blocks = (K + BK - 1) / BK;
-  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
+  const int n_tiles = (N + BN - 1) / BN;
+  int m_tiles = (M + BM - 1) / BM;
+  int total_tiles = m_tiles * n_tiles;
   // This CTA's work as a sequence of segments (tile, first K block, end K block): whole tiles
   // b, b + gridDim.x, ... or, split by K blocks, the range [u_begin, u_end) of (tile, K block) pairs.
   const bool stream_k = sk_parts != nullptr;
@@ -129,6 +130,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // (A, and C when accumulating) is touched only from here on
   pdl_wait();
   pdl_launch_dependents();
+  if (tile_group != nullptr) {
+    // The M tiles in use come first (a negative group ends them): the walk covers only those, so that every CTA gets
+    // its share of them whatever part of the rows is in use.  Every warp finds the same count.
+    int used = m_tiles;
+    for (int base = 0; base < m_tiles; base += 32) {
+      const unsigned live = __ballot_sync(0xffffffffu, base + lane < m_tiles && tile_group[min(base + lane, m_tiles - 1)] >= 0);
+      const unsigned want = m_tiles - base >= 32 ? 0xffffffffu : (1u << (m_tiles - base)) - 1u;
+      if (live != want) { used = base + __ffs(~live) - 1; break; }
+    }
+    m_tiles = used;
+    total_tiles = m_tiles * n_tiles;
+  }
 
   if (warp == 0) {
     // Producer and MMA warps walk their loops as whole warps: control flow stays warp-uniform, so
@@ -518,7 +531,8 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
 
 // Grouped product: A [M, K] holds rows in tiles of 128 (M a multiple of 128), W [groups * N, K] one [N, K] matrix per
 // group stacked by rows; C[tile i's rows] = A[tile i's rows] . W[tile_group[i]]^T, tiles with a negative group are
-// left alone.  tile_group (device, M / 128 ints) is read by the kernel, so the launch does not depend on it.
+// left alone; the tiles in use come first (everything behind the first negative entry is left alone too).  tile_group
+// (device, M / 128 ints) is read by the kernel, so the launch does not depend on it.
 // C: bfloat16 or float32 [M, ldc], stored; with `clamped` the clamped gated activation of the product (limit, alpha) instead.
 HFEE_API int hfee_gemm_tcgen05_grouped(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
                                        int out_dtype, int M, int N, int K, int groups, const int* tile_group, int clamped,

@@ -36,13 +36,17 @@ add_sinusoid_kernel(float* __restrict__ x, const int* __restrict__ positions, in
   }
 }
 
+constexpr int SOFTCAP_COLS = 4 * ROW_THREADS;
+
 __global__ void __launch_bounds__(ROW_THREADS)
 softcap_kernel(float* __restrict__ x, long long ld, int cols, float cap) {
   pdl_wait();
   pdl_launch_dependents();
   float* row = x + (long long)blockIdx.x * ld;
   const float inv = 1.f / cap;
-  for (int c = threadIdx.x; c < cols; c += ROW_THREADS) row[c] = cap * tanhf(row[c] * inv);
+  // blockIdx.y: the row's columns in pieces of SOFTCAP_COLS, so that a few rows of a large vocabulary still fill the GPU
+  const int c0 = blockIdx.y * SOFTCAP_COLS, c1 = min(cols, c0 + SOFTCAP_COLS);
+  for (int c = c0 + threadIdx.x; c < c1; c += ROW_THREADS) row[c] = cap * tanhf(row[c] * inv);
 }
 
 __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
@@ -129,7 +133,8 @@ HFEE_API int hfee_add_sinusoid(float* x, const int* positions, int n, int width,
 HFEE_API int hfee_softcap(float* x, long long ld, int rows, int cols, float cap, cudaStream_t stream) {
   if (rows == 0) return HFEE_OK;
   HFEE_REQUIRE(rows > 0 && cols > 0 && ld >= cols && cap > 0.f, "softcap: bad sizes or cap");
-  hfee_launch(softcap_kernel, dim3(rows), dim3(ROW_THREADS), 0, stream, x, ld, cols, cap);
+  HFEE_REQUIRE((cols + SOFTCAP_COLS - 1) / SOFTCAP_COLS <= 65535, "softcap: %d columns are too many", cols);
+  hfee_launch(softcap_kernel, dim3(rows, (cols + SOFTCAP_COLS - 1) / SOFTCAP_COLS), dim3(ROW_THREADS), 0, stream, x, ld, cols, cap);
   return hfee_check_launch("softcap");
 }
 

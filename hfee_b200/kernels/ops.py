@@ -1535,7 +1535,8 @@ def moe_experts_grouped_ok(x_dtype: torch.dtype, width: int, inner: int) -> bool
 def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, out: torch.Tensor,
                          clamped: Optional[tuple] = None) -> None:
     """out[rows of tile i] = a[rows of tile i] @ w[tile_group[i]].T for tiles of GROUPED_TILE_ROWS rows; tiles whose
-    group is negative are left alone.  ``a`` [tiles * 128, k] bfloat16, ``w`` [groups, n, k] bfloat16 contiguous,
+    group is negative are left alone, and so is everything behind the first of them (the tiles in use come first).
+    ``a`` [tiles * 128, k] bfloat16, ``w`` [groups, n, k] bfloat16 contiguous,
     ``out`` [tiles * 128, n] bfloat16 or float32.  ``tile_group`` is read on the device.  With ``clamped`` = (limit,
     alpha) every group's rows come in runs of [4 gate | 4 up] and ``out`` [tiles * 128, n / 2] bfloat16 receives
     :func:`clamped_glu` of the product, applied to the float32 accumulator."""
