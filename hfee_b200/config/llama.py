@@ -46,6 +46,15 @@ class RopeScaling:
         return out
 
 
+@dataclass(frozen=True)
+class LinearRopeScaling:
+    """Linear scaling of positions: every frequency is divided by ``factor``."""
+    factor: float
+
+    def apply(self, inv_freq: List[float]) -> List[float]:
+        return [w / self.factor for w in inv_freq]
+
+
 def _need(d: Mapping[str, Any], key: str) -> Any:
     if key not in d or d[key] is None:
         raise ConfigError(f"config.json: missing key {key!r}")

@@ -97,10 +97,13 @@ class RunSpec:
     several entries: its weights are shared).  ``cache`` is the id of the cache
     this run uses; runs with the same id share one cache, and only a run with
     ``writes_cache`` stores into it, so a later run can read what an earlier
-    layer cached."""
+    layer cached.  ``adds_embedding``: what the embedding left (the stream as it was in
+    front of the first run) is added to the stream right before this run, as a model does
+    that sends the stream through a stretch of layers several times over."""
     layer: int
     cache: int
     writes_cache: bool = True
+    adds_embedding: bool = False      # the embedding's output is added to the stream in front of this run
 
 
 @dataclass(frozen=True)

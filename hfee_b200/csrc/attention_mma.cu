@@ -48,8 +48,9 @@ struct AttnParams {
   // score in log2 units (ln(x) * log2(e) = log2(x): r1 is used as it is),
   // and the output times out_scale.
   PagedCache vcache;
-  const float* dist_r1; const float* dist_r2;
+  const float* dist_r1; const float* dist_r2;     // both null: no penalty
   float out_scale;
+  const float* sink;           // DIST only: per query head, one more term exp(sink[h]) of the softmax's denominator; null: none
 };
 
 // Rotates the 16-byte piece of a head that starts at dim `a` (a multiple of 8): pairs (i, i + half)
@@ -270,7 +271,7 @@ attention_mma_kernel(AttnParams p) {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int row = wrow + g + 8 * h;
-      if (row < rows_used) {
+      if (row < rows_used && p.dist_r1 != nullptr) {
         row_r1[h] = p.dist_r1[kvh * p.group + row % p.group];
         row_r2[h] = p.dist_r2[kvh * p.group + row % p.group];
       }
@@ -387,14 +388,21 @@ attention_mma_kernel(AttnParams p) {
     // softmax on the raw scores: p = 2^(s*c - m*c) with c = scale*log2(e) folded into one FMA
     const int key0 = b * BLOCK_N + wkey;                       // first key this warp visits in the block
     if constexpr (DIST) {
+      if (p.dist_r1 != nullptr) {
 #pragma unroll
-      for (int nt = 0; nt < WKEYS / 8; ++nt)
+        for (int nt = 0; nt < WKEYS / 8; ++nt)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int h = j >> 1;
-          const float dist = (float)max(row_pos[h] - (key0 + nt * 8 + 2 * c + (j & 1)), 0);
-          s[nt][j] = fmaf(s[nt][j], p.scale_log2, -row_r1[h] * __log2f(fmaf(row_r2[h], dist, 1.f)));
-        }
+          for (int j = 0; j < 4; ++j) {
+            const int h = j >> 1;
+            const float dist = (float)max(row_pos[h] - (key0 + nt * 8 + 2 * c + (j & 1)), 0);
+            s[nt][j] = fmaf(s[nt][j], p.scale_log2, -row_r1[h] * __log2f(fmaf(row_r2[h], dist, 1.f)));
+          }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < WKEYS / 8; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) s[nt][j] *= p.scale_log2;
+      }
     }
     const int row_lo = min(row_pos_min, row_pos_max), row_hi = row_pos_max;
     const bool need_mask = key0 + WKEYS - 1 > row_lo || (p.window > 0 && key0 <= row_hi - p.window);
@@ -504,6 +512,8 @@ attention_mma_kernel(AttnParams p) {
       }
       int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
       if (p.num_splits == 1) {
+        if constexpr (DIST)
+          if (p.sink != nullptr && m != -INFINITY) l += exp2f(p.sink[head] * 1.4426950408889634f - m);
         float inv = l > 0.f ? 1.f / l : 0.f;
         if constexpr (DIST) inv *= p.out_scale;
         __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * vdim;
@@ -521,6 +531,8 @@ attention_mma_kernel(AttnParams p) {
     if (row >= rows_used) continue;
     int t = t_first + row / p.group, head = kvh * p.group + row % p.group;
     if (p.num_splits == 1) {
+      if constexpr (DIST)          // m_run is in log2 units here
+        if (p.sink != nullptr && m_run[h] != -INFINITY) l_run[h] += exp2f(p.sink[head] * 1.4426950408889634f - m_run[h]);
       float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
       if constexpr (DIST) inv *= p.out_scale;
       __nv_bfloat16* dst = p.out + (long long)(tok0 + t) * p.ld_o + (long long)head * vdim;
@@ -552,7 +564,7 @@ constexpr int COMBINE_WARPS = 4;
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                          __nv_bfloat16* __restrict__ out, int ld_o, int heads, int hd, int num_splits, int pairs,
-                         int stride, float out_scale) {      // stride: floats per partial output (>= hd, a multiple of 4)
+                         int stride, float out_scale, const float* __restrict__ sink) {      // stride: floats per partial output (>= hd, a multiple of 4); sink: per head or null
   pdl_wait();
   pdl_launch_dependents();
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -581,6 +593,7 @@ attention_combine_kernel(const float* __restrict__ part_o, const float* __restri
         w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m);
         float l = 0.f;
         for (int s = 0; s < num_splits; ++s) l += __shfl_sync(0xffffffffu, w * ml.y, s);     // split order
+        if (sink != nullptr && m != -INFINITY) l += exp2f(sink[head] * 1.4426950408889634f - m);
         inv = l > 0.f ? out_scale / l : 0.f;
         have_w = true;
       }
@@ -644,7 +657,7 @@ struct RopeFusion {
 };
 // A penalty on distance and sizes of their own for keys and values (head_dim of the call is then the tile size)
 struct DistanceOption {
-  int key_dim, value_dim; const float* r1; const float* r2; float out_scale;
+  int key_dim, value_dim; const float* r1; const float* r2; float out_scale; const float* sink;
 };
 
 int attention_mma_impl(const void* q, int ld_q, const void* k_pool, const void* v_pool,
@@ -681,6 +694,7 @@ int attention_mma_impl(const void* q, int ld_q, const void* k_pool, const void* 
                "attention_mma: page_size %d must be a power of two", page_size);
   make_paged_cache(&p.vcache, block_table, max_pages, page_size, kv_heads, dist ? dist->value_dim : head_dim);
   p.dist_r1 = dist ? dist->r1 : nullptr; p.dist_r2 = dist ? dist->r2 : nullptr; p.out_scale = dist ? dist->out_scale : 1.f;
+  p.sink = dist ? dist->sink : nullptr;
   p.cu_tokens = cu_tokens; p.slots = slots; p.context_before = context_before;
   p.heads = heads; p.group = group;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -721,7 +735,7 @@ int attention_mma_impl(const void* q, int ld_q, const void* k_pool, const void* 
   int pairs = n_tokens * heads;
   hfee_launch(attention_combine_kernel, dim3((unsigned)((pairs + COMBINE_WARPS - 1) / COMBINE_WARPS)),
               dim3(COMBINE_WARPS * 32), 0, stream, p.part_o, p.part_ml, p.out, ld_o, heads, dist ? dist->value_dim : head_dim,
-              num_splits, pairs, head_dim, p.out_scale);
+              num_splits, pairs, head_dim, p.out_scale, p.sink);
   return hfee_check_launch("attention_combine");
 }
 }  // namespace
@@ -764,7 +778,24 @@ HFEE_API int hfee_attention_mma_distance(const void* q, int ld_q, const void* k_
   const int tile = hfee_attention_mma_distance_tile(key_dim, value_dim);
   HFEE_REQUIRE(tile > 0, "attention_mma_distance: key size %d and value size %d must be multiples of 8 up to 256", key_dim, value_dim);
   HFEE_REQUIRE(r1 != nullptr && r2 != nullptr, "attention_mma_distance: the penalty needs both of its arrays");
-  DistanceOption dist{key_dim, value_dim, r1, r2, out_scale};
+  DistanceOption dist{key_dim, value_dim, r1, r2, out_scale, nullptr};
+  return attention_mma_impl(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, cu_tokens, slots, context_before,
+                            out, ld_o, n_tokens, requests, max_new, heads, kv_heads, tile, scale, window, num_splits,
+                            scratch, nullptr, stream, &dist);
+}
+
+// hfee_attention_mma_distance with the penalty optional (r1 and r2 both null: none) and an optional sink: with
+// `sink` (float32 per query head) the softmax's denominator also holds exp(sink[h]), a term without key or value.
+HFEE_API int hfee_attention_mma_general(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                        const int* block_table, int max_pages, int page_size, const int* cu_tokens,
+                                        const int* slots, const int* context_before, void* out, int ld_o, int n_tokens,
+                                        int requests, int max_new, int heads, int kv_heads, int key_dim, int value_dim,
+                                        float scale, const float* r1, const float* r2, const float* sink, float out_scale,
+                                        int window, int num_splits, float* scratch, cudaStream_t stream) {
+  const int tile = hfee_attention_mma_distance_tile(key_dim, value_dim);
+  HFEE_REQUIRE(tile > 0, "attention_mma_general: key size %d and value size %d must be multiples of 8 up to 256", key_dim, value_dim);
+  HFEE_REQUIRE((r1 == nullptr) == (r2 == nullptr), "attention_mma_general: the penalty needs both of its arrays");
+  DistanceOption dist{key_dim, value_dim, r1, r2, out_scale, sink};
   return attention_mma_impl(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, cu_tokens, slots, context_before,
                             out, ld_o, n_tokens, requests, max_new, heads, kv_heads, tile, scale, window, num_splits,
                             scratch, nullptr, stream, &dist);

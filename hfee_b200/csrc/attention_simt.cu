@@ -34,7 +34,8 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
                       const int* __restrict__ slot_of_token, T* __restrict__ out, int ld_o, int n, int heads,
                       float scale, int window, int chunk, const float* __restrict__ head_scale,
                       const float* __restrict__ head_bias, const T* __restrict__ gate, long long ld_gate,
-                      int gate_mode, const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, float out_scale) {
+                      int gate_mode, const float* __restrict__ dist_r1, const float* __restrict__ dist_r2, float out_scale,
+                      const float* __restrict__ sink) {
   pdl_wait();
   pdl_launch_dependents();
   __shared__ float q_s[WARPS][MAX_HD];
@@ -59,7 +60,8 @@ attention_simt_kernel(const T* __restrict__ q, int ld_q, const T* __restrict__ k
   float o[DPL];
 #pragma unroll
   for (int j = 0; j < DPL; ++j) o[j] = 0.f;
-  float m = -INFINITY, l = 0.f;
+  // a sink is one more term exp(sink[h]) of the denominator that has no key and no value
+  float m = (!SIGMOID && sink != nullptr) ? sink[h] : -INFINITY, l = (!SIGMOID && sink != nullptr) ? 1.f : 0.f;
 
   for (int base = lo; base <= pos; base += 32) {
     int key = base + lane;
@@ -117,17 +119,17 @@ void launch_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool
                  int vd, const int* positions,
                  const int* slot_of_token, void* out, int ld_o, int n, int heads, float scale, int window, int chunk,
                  int sigmoid, const float* head_scale, const float* head_bias, const void* gate, long long ld_gate,
-                 int gate_mode, const float* dist_r1, const float* dist_r2, float out_scale, cudaStream_t stream) {
+                 int gate_mode, const float* dist_r1, const float* dist_r2, float out_scale, const float* sink, cudaStream_t stream) {
   long long tasks = (long long)n * heads;
   unsigned blocks = (unsigned)((tasks + WARPS - 1) / WARPS);
   if (sigmoid)
     hfee_launch(attention_simt_kernel<T, true>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const T*)q, ld_q, (const T*)k_pool,
                 (const T*)v_pool, c, vc, vd, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
-                head_bias, (const T*)gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale);
+                head_bias, (const T*)gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale, sink);
   else
     hfee_launch(attention_simt_kernel<T, false>, dim3(blocks), dim3(WARPS * 32), 0, stream, (const T*)q, ld_q, (const T*)k_pool,
                 (const T*)v_pool, c, vc, vd, positions, slot_of_token, (T*)out, ld_o, n, heads, scale, window, chunk, head_scale,
-                head_bias, (const T*)gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale);
+                head_bias, (const T*)gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale, sink);
 }
 }  // namespace
 
@@ -136,14 +138,17 @@ void launch_simt(const void* q, int ld_q, const void* k_pool, const void* v_pool
 // pool itself, whose leading value_dim dimensions are the values.  gate_mode: 0 none, 1 one number per output
 // element ([n, heads * value_dim]), 2 one number per head ([n, heads]); the output is multiplied by its sigmoid.
 // dist_r1, dist_r2 (per head, or both null): r1[h] * ln(1 + r2[h] * (query position - key position)) is taken off the
-// score before the softmax.  out_scale multiplies the output.
-HFEE_API int hfee_attention_simt_distance(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+// score before the softmax.  out_scale multiplies the output.  sink (per head, or null): the softmax's denominator also
+// holds exp(sink[h]).
+HFEE_API int hfee_attention_simt_sink(const void* q, int ld_q, const void* k_pool, const void* v_pool,
                                           const int* block_table, int max_pages, int page_size, const int* positions,
                                           const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
                                           int head_dim, int value_dim, int values_in_keys, float scale, int window,
                                           int chunk, int weights, const float* head_scale, const float* head_bias,
                                           const void* gate, long long ld_gate, int gate_mode, const float* dist_r1,
-                                          const float* dist_r2, float out_scale, int dtype, cudaStream_t stream) {
+                                          const float* dist_r2, float out_scale, const float* sink, int dtype,
+                                          cudaStream_t stream) {
+  HFEE_REQUIRE(sink == nullptr || weights == 0, "attention_simt: a sink goes with the softmax");
   HFEE_REQUIRE((dist_r1 == nullptr) == (dist_r2 == nullptr), "attention_simt: the distance penalty needs both of its arrays");
   HFEE_REQUIRE(dist_r1 == nullptr || weights == 0, "attention_simt: the distance penalty goes with the softmax");
   if (n == 0) return HFEE_OK;
@@ -169,14 +174,27 @@ HFEE_API int hfee_attention_simt_distance(const void* q, int ld_q, const void* k
   }
   if (dtype == HFEE_F32)
     launch_simt<float>(q, ld_q, k_pool, v_pool, c, vc, value_dim, positions, slot_of_token, out, ld_o, n, heads, scale,
-                       window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale, stream);
+                       window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale, sink, stream);
   else if (dtype == HFEE_BF16)
     launch_simt<__nv_bfloat16>(q, ld_q, k_pool, v_pool, c, vc, value_dim, positions, slot_of_token, out, ld_o, n, heads,
                                scale, window, chunk, weights, head_scale, head_bias, gate, ld_gate, gate_mode, dist_r1, dist_r2,
-                               out_scale, stream);
+                               out_scale, sink, stream);
   else
     return hfee_fail(HFEE_ERR_ARG, "attention_simt: unknown dtype %d", dtype);
   return hfee_check_launch("attention_simt");
+}
+
+HFEE_API int hfee_attention_simt_distance(const void* q, int ld_q, const void* k_pool, const void* v_pool,
+                                          const int* block_table, int max_pages, int page_size, const int* positions,
+                                          const int* slot_of_token, void* out, int ld_o, int n, int heads, int kv_heads,
+                                          int head_dim, int value_dim, int values_in_keys, float scale, int window,
+                                          int chunk, int weights, const float* head_scale, const float* head_bias,
+                                          const void* gate, long long ld_gate, int gate_mode, const float* dist_r1,
+                                          const float* dist_r2, float out_scale, int dtype, cudaStream_t stream) {
+  return hfee_attention_simt_sink(q, ld_q, k_pool, v_pool, block_table, max_pages, page_size, positions, slot_of_token, out,
+                                  ld_o, n, heads, kv_heads, head_dim, value_dim, values_in_keys, scale, window, chunk,
+                                  weights, head_scale, head_bias, gate, ld_gate, gate_mode, dist_r1, dist_r2, out_scale,
+                                  nullptr, dtype, stream);
 }
 
 HFEE_API int hfee_attention_simt_general(const void* q, int ld_q, const void* k_pool, const void* v_pool,

@@ -454,8 +454,8 @@ HFEE_API int hfee_qk_norm_rope_cache(const void* qk, long long ld_qk, const floa
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-//   hfee_head_norm_gate   per (token, head): out = x / sqrt(mean_head(x^2) + eps) * w[d] * act(gate), the weight
-//                         [head_dim] shared by the heads; act = sigmoid or SiLU
+//   hfee_head_norm_gate   per (token, head): out = x / sqrt(mean_head(x^2) + eps) * w[d] * act(gate) * out_scale, the weight
+//                         [head_dim] shared by the heads, or [heads * head_dim] (w_head_stride = head_dim); act = sigmoid or SiLU
 //   hfee_unary_act        out = act(x) element by element; act = relu(x)^2
 //   hfee_head_gate        x[i, h, :] *= sigmoid(gate[i, h]): one gate number per head
 namespace {
@@ -467,7 +467,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ x, long long ld_x, const float* __restrict__ w, float eps,
                       const T* __restrict__ gate, long long ld_g, T* __restrict__ out, long long ld_o, int n, int heads,
-                      int head_dim, int act) {
+                      int head_dim, int act, int w_head_stride, float out_scale) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -479,11 +479,12 @@ head_norm_gate_kernel(const float* __restrict__ x, long long ld_x, const float* 
   T* orow = out + (long long)i * ld_o + (long long)h * head_dim;
   float ss = 0.f;
   for (int d = lane; d < head_dim; d += 32) ss = fmaf(xr[d], xr[d], ss);
-  const float scale = 1.0f / sqrtf(warp_sum(ss) / (float)head_dim + eps);
+  const float scale = out_scale / sqrtf(warp_sum(ss) / (float)head_dim + eps);
+  const float* wh = w + (long long)h * w_head_stride;
   for (int d = lane; d < head_dim; d += 32) {
     const float g = to_f32<T>(gr[d]);
     const float s = sigmoid_f32(g);
-    orow[d] = from_f32<T>(xr[d] * scale * w[d] * (act == HG_SILU ? g * s : s));
+    orow[d] = from_f32<T>(xr[d] * scale * wh[d] * (act == HG_SILU ? g * s : s));
   }
 }
 
@@ -517,22 +518,29 @@ head_gate_kernel(T* __restrict__ x, long long ld_x, const T* __restrict__ gate, 
 
 }  // namespace
 
-HFEE_API int hfee_head_norm_gate(const float* x, long long ld_x, const float* w, float eps, const void* gate, long long ld_g,
-                                 void* out, long long ld_o, int n, int heads, int head_dim, int act, int dtype,
-                                 cudaStream_t stream) {
+HFEE_API int hfee_head_norm_gate_scaled(const float* x, long long ld_x, const float* w, int w_per_head, float eps, const void* gate,
+                                        long long ld_g, void* out, long long ld_o, int n, int heads, int head_dim, int act,
+                                        float out_scale, int dtype, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
+  const int w_head_stride = w_per_head ? head_dim : 0;
   const long long width = (long long)heads * head_dim;
   HFEE_REQUIRE(n > 0 && heads > 0 && head_dim > 0 && ld_x >= width && ld_g >= width && ld_o >= width, "head_norm_gate: bad sizes");
   HFEE_REQUIRE(act == HG_SIGMOID || act == HG_SILU, "head_norm_gate: unknown gate activation %d", act);
   HFEE_REQUIRE((long long)n * heads < (1ll << 31), "head_norm_gate: too many (token, head) pairs for one launch");
   const unsigned blocks = (unsigned)(((long long)n * heads + 3) / 4);
   if (dtype == HFEE_F32)
-    hfee_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(128), 0, stream, x, ld_x, w, eps, (const float*)gate, ld_g, (float*)out, ld_o, n, heads, head_dim, act);
+    hfee_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(128), 0, stream, x, ld_x, w, eps, (const float*)gate, ld_g, (float*)out, ld_o, n, heads, head_dim, act, w_head_stride, out_scale);
   else if (dtype == HFEE_BF16)
-    hfee_launch(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, x, ld_x, w, eps, (const __nv_bfloat16*)gate, ld_g, (__nv_bfloat16*)out, ld_o, n, heads, head_dim, act);
+    hfee_launch(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, stream, x, ld_x, w, eps, (const __nv_bfloat16*)gate, ld_g, (__nv_bfloat16*)out, ld_o, n, heads, head_dim, act, w_head_stride, out_scale);
   else
     return hfee_fail(HFEE_ERR_ARG, "head_norm_gate: unknown dtype %d", dtype);
   return hfee_check_launch("head_norm_gate");
+}
+
+HFEE_API int hfee_head_norm_gate(const float* x, long long ld_x, const float* w, float eps, const void* gate, long long ld_g,
+                                 void* out, long long ld_o, int n, int heads, int head_dim, int act, int dtype,
+                                 cudaStream_t stream) {
+  return hfee_head_norm_gate_scaled(x, ld_x, w, 0, eps, gate, ld_g, out, ld_o, n, heads, head_dim, act, 1.f, dtype, stream);
 }
 
 HFEE_API int hfee_unary_act(const void* x, long long ld_x, void* out, long long ld_o, int rows, int cols, int act, int dtype,

@@ -1,0 +1,226 @@
+// Linear attention whose matrix state is gated by the token, with a float32 state per (request, head):
+//
+//   channel decay      S_t = diag(a_t) S_(t-1) + k_t v_t^T            a_t = sigmoid(z_t)^(1/tau) per key channel
+//                      o_t = S_t^T q_t
+//
+//   exponential gates  m_t = max(f_t + m_(t-1), i_t)                  i_t = cap tanh(x_i / cap), f_t = logsigmoid(cap tanh(x_f / cap))
+//                      S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) + e^(i_t - m_t) k_t v_t^T          (n_t the same with k_t alone)
+//                      o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
+//
+// S: [dim][vdim], n: [dim], m: one number; all zero for a fresh request.  q (times q_scale), k and v are slices of one
+// projection buffer (type T); the gates' pre-activations z, x_i, x_f are float32, and so are the decays, their
+// logarithms and exponentials, the states, every product and o.
+//
+// hfee_gated_recurrence walks a request's tokens one after the other.  A thread keeps GR_ROWS rows of one state
+// column in registers; a warp covers GR_COLS = 32 columns of those rows, a block all rows (blockDim.y row groups whose
+// partial outputs meet in shared memory in a fixed order) of 32 columns; blockIdx = (head, request, column tile).
+// Lane j of row group g also keeps n[g * 32 + j].  Tokens are staged GR_STAGE at a time; the scalar recurrence of
+// the running maximum is walked by one thread per stage.  The order of the sums does not depend on how a prompt was
+// cut, and a state is what the tokens before left, so neither does a position's output.
+#include "common.cuh"
+
+namespace {
+
+constexpr int GR_ROWS = 32;
+constexpr int GR_COLS = 32;
+constexpr int GR_STAGE = 8;
+constexpr int GR_MAX_DIM = 256;
+
+enum Mode { MODE_CHANNEL_DECAY = 0, MODE_EXP_GATES = 1 };
+
+__device__ __forceinline__ float log_sigmoid_f32(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+struct RecurrenceArgs {
+  long long ld;                 // of q, k, v
+  const float* pre;             // channel decay: z [n, heads * dim]; exponential gates: [n, 2 * heads] = x_i then x_f
+  long long ld_pre;
+  const float* bias;            // added to `pre` column by column; may be null
+  float p0;                     // channel decay: 1 / tau; exponential gates: cap
+  float q_scale;
+  float* state;                 // [slots, heads, dim, vdim]
+  float* norm_state;            // [slots, heads, dim]       (exponential gates)
+  float* max_state;             // [slots, heads]            (exponential gates)
+  const int* cu_tokens;
+  const int* slots;
+  float* out;
+  long long ld_o;
+  int heads, dim, vdim, write_state;
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(GR_COLS * (GR_MAX_DIM / GR_ROWS))
+gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, RecurrenceArgs p) {
+  extern __shared__ __align__(16) float smem[];
+  __shared__ float a_s[GR_STAGE], b_s[GR_STAGE], em_s[GR_STAGE];
+  __shared__ float m_cur;
+  const int head = blockIdx.x, req = blockIdx.y;
+  const int groups = blockDim.y, dim_pad = groups * GR_ROWS;
+  const int j = threadIdx.x, g = threadIdx.y;
+  const int col = blockIdx.z * GR_COLS + j;
+  const int tid = g * GR_COLS + j, threads = GR_COLS * groups;
+  const int heads = p.heads, dim = p.dim, vdim = p.vdim;
+  float* qs = smem;                                   // [GR_STAGE][dim_pad]
+  float* ks = qs + GR_STAGE * dim_pad;                // [GR_STAGE][dim_pad]
+  float* vs = ks + GR_STAGE * dim_pad;                // [GR_STAGE][GR_COLS]
+  float* part = vs + GR_STAGE * GR_COLS;              // [GR_STAGE][groups][GR_COLS]
+  float* part_n = part + GR_STAGE * groups * GR_COLS; // [GR_STAGE][groups]
+  float* as = part_n + GR_STAGE * groups;             // [GR_STAGE][dim_pad]   (channel decay)
+  const int begin = p.cu_tokens[req], count = p.cu_tokens[req + 1] - begin;
+  const int slot = p.slots[req];
+  pdl_wait();
+  pdl_launch_dependents();
+  if (count <= 0) return;
+
+  float* S_g = p.state + (((long long)slot * heads + head) * dim) * vdim;
+  float S[GR_ROWS];
+#pragma unroll
+  for (int i = 0; i < GR_ROWS; ++i) {
+    const int row = g * GR_ROWS + i;
+    S[i] = (row < dim && col < vdim) ? S_g[(long long)row * vdim + col] : 0.f;
+  }
+  float n_own = 0.f;                                  // n[g * GR_ROWS + j]
+  const int own_row = g * GR_ROWS + j;
+  if constexpr (MODE == MODE_EXP_GATES) {
+    if (own_row < dim) n_own = p.norm_state[((long long)slot * heads + head) * dim + own_row];
+    if (tid == 0) m_cur = p.max_state[(long long)slot * heads + head];
+  }
+  for (int t0 = 0; t0 < count; t0 += GR_STAGE) {
+    const int nt = min(GR_STAGE, count - t0);
+    __syncthreads();                                  // the stage before is used up
+    for (int e = tid; e < nt * dim_pad; e += threads) {
+      const int t = e / dim_pad, d = e % dim_pad;
+      const long long at = (long long)(begin + t0 + t) * p.ld + (long long)head * dim + d;
+      qs[e] = d < dim ? to_f32<T>(q[at]) * p.q_scale : 0.f;
+      ks[e] = d < dim ? to_f32<T>(k[at]) : 0.f;
+      if constexpr (MODE == MODE_CHANNEL_DECAY) {
+        float a = 1.f;
+        if (d < dim) {
+          const int c = head * dim + d;
+          const float z = p.pre[(long long)(begin + t0 + t) * p.ld_pre + c] + (p.bias != nullptr ? p.bias[c] : 0.f);
+          a = expf(log_sigmoid_f32(z) * p.p0);
+        }
+        as[e] = a;
+      }
+    }
+    for (int e = tid; e < nt * GR_COLS; e += threads) {
+      const int t = e / GR_COLS, c = blockIdx.z * GR_COLS + e % GR_COLS;
+      vs[e] = c < vdim ? to_f32<T>(v[(long long)(begin + t0 + t) * p.ld + (long long)head * vdim + c]) : 0.f;
+    }
+    if constexpr (MODE == MODE_EXP_GATES) {
+      if (tid == 0) {
+        float m = m_cur;
+        const float cap = p.p0;
+        for (int t = 0; t < nt; ++t) {
+          const float* pre = p.pre + (long long)(begin + t0 + t) * p.ld_pre;
+          const float xi = pre[head] + (p.bias != nullptr ? p.bias[head] : 0.f);
+          const float xf = pre[heads + head] + (p.bias != nullptr ? p.bias[heads + head] : 0.f);
+          const float ig = cap * tanhf(xi / cap);
+          const float fg = log_sigmoid_f32(cap * tanhf(xf / cap));
+          const float m_new = fmaxf(fg + m, ig);
+          a_s[t] = expf(fg + m - m_new);
+          b_s[t] = expf(ig - m_new);
+          em_s[t] = expf(-m_new);
+          m = m_new;
+        }
+        m_cur = m;
+      }
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const float vv = vs[t * GR_COLS + j];
+      const float4* k4 = reinterpret_cast<const float4*>(ks + t * dim_pad + g * GR_ROWS);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + t * dim_pad + g * GR_ROWS);
+      float acc = 0.f;
+      if constexpr (MODE == MODE_CHANNEL_DECAY) {
+        const float4* a4 = reinterpret_cast<const float4*>(as + t * dim_pad + g * GR_ROWS);
+#pragma unroll
+        for (int i = 0; i < GR_ROWS / 4; ++i) {
+          const float4 kk = k4[i], qq = q4[i], aa = a4[i];
+          S[4 * i + 0] = fmaf(aa.x, S[4 * i + 0], kk.x * vv);  acc = fmaf(S[4 * i + 0], qq.x, acc);
+          S[4 * i + 1] = fmaf(aa.y, S[4 * i + 1], kk.y * vv);  acc = fmaf(S[4 * i + 1], qq.y, acc);
+          S[4 * i + 2] = fmaf(aa.z, S[4 * i + 2], kk.z * vv);  acc = fmaf(S[4 * i + 2], qq.z, acc);
+          S[4 * i + 3] = fmaf(aa.w, S[4 * i + 3], kk.w * vv);  acc = fmaf(S[4 * i + 3], qq.w, acc);
+        }
+      } else {
+        const float a = a_s[t], bv = b_s[t] * vv;
+#pragma unroll
+        for (int i = 0; i < GR_ROWS / 4; ++i) {
+          const float4 kk = k4[i], qq = q4[i];
+          S[4 * i + 0] = fmaf(a, S[4 * i + 0], kk.x * bv);  acc = fmaf(S[4 * i + 0], qq.x, acc);
+          S[4 * i + 1] = fmaf(a, S[4 * i + 1], kk.y * bv);  acc = fmaf(S[4 * i + 1], qq.y, acc);
+          S[4 * i + 2] = fmaf(a, S[4 * i + 2], kk.z * bv);  acc = fmaf(S[4 * i + 2], qq.z, acc);
+          S[4 * i + 3] = fmaf(a, S[4 * i + 3], kk.w * bv);  acc = fmaf(S[4 * i + 3], qq.w, acc);
+        }
+        n_own = fmaf(a, n_own, b_s[t] * ks[t * dim_pad + own_row]);
+        const float nq = warp_sum(n_own * qs[t * dim_pad + own_row]);
+        if (j == 0) part_n[t * groups + g] = nq;
+      }
+      part[(t * groups + g) * GR_COLS + j] = acc;
+    }
+    __syncthreads();
+    for (int e = tid; e < nt * GR_COLS; e += threads) {
+      const int t = e / GR_COLS, jj = e % GR_COLS, c = blockIdx.z * GR_COLS + jj;
+      float sum = 0.f;
+      for (int gg = 0; gg < groups; ++gg) sum += part[(t * groups + gg) * GR_COLS + jj];
+      if constexpr (MODE == MODE_EXP_GATES) {
+        float nq = 0.f;
+        for (int gg = 0; gg < groups; ++gg) nq += part_n[t * groups + gg];
+        sum /= fmaxf(fabsf(nq), em_s[t]) + 1e-6f;
+      }
+      if (c < vdim) p.out[(long long)(begin + t0 + t) * p.ld_o + (long long)head * vdim + c] = sum;
+    }
+  }
+  if (p.write_state) {
+#pragma unroll
+    for (int i = 0; i < GR_ROWS; ++i) {
+      const int row = g * GR_ROWS + i;
+      if (row < dim && col < vdim) S_g[(long long)row * vdim + col] = S[i];
+    }
+    if constexpr (MODE == MODE_EXP_GATES) {
+      if (blockIdx.z == 0) {
+        if (own_row < dim) p.norm_state[((long long)slot * heads + head) * dim + own_row] = n_own;
+        if (tid == 0) p.max_state[(long long)slot * heads + head] = m_cur;
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_recurrence(int mode, const void* q, const void* k, const void* v, const RecurrenceArgs& p, int requests,
+                      cudaStream_t stream) {
+  const int groups = (p.dim + GR_ROWS - 1) / GR_ROWS, dim_pad = groups * GR_ROWS;
+  const dim3 grid(p.heads, requests, (p.vdim + GR_COLS - 1) / GR_COLS), block(GR_COLS, groups);
+  size_t floats = (size_t)GR_STAGE * (2 * dim_pad + GR_COLS + groups * GR_COLS + groups);
+  if (mode == MODE_CHANNEL_DECAY) floats += (size_t)GR_STAGE * dim_pad;
+  const size_t smem = floats * sizeof(float);
+  if (mode == MODE_CHANNEL_DECAY)
+    hfee_launch(gated_recurrence_kernel<T, MODE_CHANNEL_DECAY>, grid, block, smem, stream, (const T*)q, (const T*)k, (const T*)v, p);
+  else
+    hfee_launch(gated_recurrence_kernel<T, MODE_EXP_GATES>, grid, block, smem, stream, (const T*)q, (const T*)k, (const T*)v, p);
+  return hfee_check_launch("gated_recurrence");
+}
+
+}  // namespace
+
+// mode 0 (channel decay): pre = z [n, heads * dim] float32 (+ bias [heads * dim] or null), p0 = 1 / tau; norm_state and
+// max_state are unused.  mode 1 (exponential gates): pre [n, 2 * heads] float32 = the input gates' pre-activations, then
+// the forget gates' (+ bias [2 * heads] or null), p0 = cap.  q, k: heads * dim columns, v: heads * vdim columns of rows
+// with the stride ld; out [n, heads * vdim] float32.  Requests without tokens in this step are skipped.
+HFEE_API int hfee_gated_recurrence(int mode, const void* q, const void* k, const void* v, long long ld, int dtype,
+                                   const float* pre, long long ld_pre, const float* bias, float p0, float q_scale,
+                                   float* state, float* norm_state, float* max_state, const int* cu_tokens,
+                                   const int* slots, float* out, long long ld_o, int requests, int heads, int dim,
+                                   int vdim, int write_state, cudaStream_t stream) {
+  if (requests == 0) return HFEE_OK;
+  HFEE_REQUIRE(mode == MODE_CHANNEL_DECAY || mode == MODE_EXP_GATES, "gated_recurrence: unknown mode %d", mode);
+  HFEE_REQUIRE(heads > 0 && dim > 0 && vdim > 0 && dim <= GR_MAX_DIM, "gated_recurrence: key size %d is outside 1..%d", dim, GR_MAX_DIM);
+  HFEE_REQUIRE(requests <= 65535 && (vdim + GR_COLS - 1) / GR_COLS <= 65535, "gated_recurrence: too many requests or columns for one grid");
+  HFEE_REQUIRE(ld_o >= (long long)heads * vdim, "gated_recurrence: ld_o is too small");
+  HFEE_REQUIRE(mode == MODE_CHANNEL_DECAY ? ld_pre >= (long long)heads * dim : ld_pre >= 2 * heads, "gated_recurrence: ld_pre is too small");
+  HFEE_REQUIRE(mode == MODE_CHANNEL_DECAY || (norm_state != nullptr && max_state != nullptr), "gated_recurrence: exponential gates need their normaliser and maximum states");
+  HFEE_REQUIRE(p0 > 0.f, "gated_recurrence: the temperature or cap must be positive");
+  RecurrenceArgs p{ld, pre, ld_pre, bias, p0, q_scale, state, norm_state, max_state, cu_tokens, slots, out, ld_o, heads, dim, vdim, write_state};
+  if (dtype == HFEE_F32) return launch_recurrence<float>(mode, q, k, v, p, requests, stream);
+  if (dtype == HFEE_BF16) return launch_recurrence<__nv_bfloat16>(mode, q, k, v, p, requests, stream);
+  return hfee_fail(HFEE_ERR_ARG, "gated_recurrence: unknown dtype %d", dtype);
+}

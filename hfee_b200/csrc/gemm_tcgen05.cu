@@ -310,7 +310,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               if constexpr (EPI == EPI_CLAMPED) {
                 gate = fminf(gate, rope.act_limit);
                 up = fminf(fmaxf(up, -rope.act_limit), rope.act_limit);
-                o[gq * 4 + i] = __fdividef(gate, 1.f + __expf(-rope.act_alpha * gate)) * (up + 1.f);
+                o[gq * 4 + i] = __fdividef(gate, 1.f + __expf(-rope.act_alpha * gate)) * (up + rope.act_shift);
               } else {
                 o[gq * 4 + i] = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
               }
@@ -536,7 +536,7 @@ HFEE_API int hfee_gemm_tcgen05(const void* A, long long lda, const void* W, long
 // C: bfloat16 or float32 [M, ldc], stored; with `clamped` the clamped gated activation of the product (limit, alpha) instead.
 HFEE_API int hfee_gemm_tcgen05_grouped(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
                                        int out_dtype, int M, int N, int K, int groups, const int* tile_group, int clamped,
-                                       float limit, float alpha, int* status, cudaStream_t stream) {
+                                       float limit, float alpha, float shift, int* status, cudaStream_t stream) {
   if (M == 0 || N == 0) return HFEE_OK;
   HFEE_REQUIRE(M > 0 && M % BM == 0 && N > 0 && K > 0 && K % 8 == 0 && groups > 0 && tile_group != nullptr,
                "gemm_tcgen05_grouped: M=%d must be a multiple of 128 and K=%d a multiple of 8", M, K);
@@ -557,6 +557,7 @@ HFEE_API int hfee_gemm_tcgen05_grouped(const void* A, long long lda, const void*
     RopeEpi par = RopeEpi{};
     par.act_limit = limit;
     par.act_alpha = alpha;
+    par.act_shift = shift;
     if (bn == 256) return launch<256, EPI_CLAMPED, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, par, tile_group, N);
     return launch<128, EPI_CLAMPED, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, nullptr, 0, nullptr, stream, par, tile_group, N);
   }

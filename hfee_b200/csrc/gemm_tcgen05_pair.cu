@@ -236,7 +236,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
               if constexpr (EPI == EPI_CLAMPED) {
                 gate = fminf(gate, rope.act_limit);
                 up = fminf(fmaxf(up, -rope.act_limit), rope.act_limit);
-                o[gq * 4 + i] = __fdividef(gate, 1.f + __expf(-rope.act_alpha * gate)) * (up + 1.f);
+                o[gq * 4 + i] = __fdividef(gate, 1.f + __expf(-rope.act_alpha * gate)) * (up + rope.act_shift);
               } else {
                 o[gq * 4 + i] = (EPI == EPI_GEGLU ? gelu_tanh_gate_fast(gate) : __fdividef(gate, 1.f + __expf(-gate))) * up;
               }
@@ -423,7 +423,7 @@ HFEE_API int hfee_gemm_tcgen05_pair(const void* A, long long lda, const void* W,
 // The gate/up product of a clamped gated feed-forward: W rows in groups of [4 gate | 4 up], C [M, N/2] bfloat16 =
 // g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), applied to the float32 accumulator.
 HFEE_API int hfee_gemm_tcgen05_pair_clamped(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc,
-                                            int M, int N, int K, float limit, float alpha, int* status, cudaStream_t stream) {
+                                            int M, int N, int K, float limit, float alpha, float shift, int* status, cudaStream_t stream) {
   if (M == 0 || N == 0) return HFEE_OK;
   HFEE_REQUIRE(M > 0 && N > 0 && N % 8 == 0 && K > 0 && K % 8 == 0, "gemm_tcgen05_pair_clamped: N=%d and K=%d must be positive multiples of 8", N, K);
   HFEE_REQUIRE(lda % 8 == 0 && ldw % 8 == 0 && lda >= K && ldw >= K && ldc >= N / 2,
@@ -437,6 +437,7 @@ HFEE_API int hfee_gemm_tcgen05_pair_clamped(const void* A, long long lda, const 
   RopeEpi par = RopeEpi{};
   par.act_limit = limit;
   par.act_alpha = alpha;
+  par.act_shift = shift;
   return launch_pair<256, EPI_CLAMPED, __nv_bfloat16>(ma, mw, C, ldc, M, N, K, status, stream, par);
 }
 

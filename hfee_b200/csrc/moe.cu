@@ -20,7 +20,7 @@
 // live in device memory, so a step replays from a CUDA graph.  A pair's result is computed by one thread block
 // with k summed in order and does not depend on its place, so the order inside an expert (which the plan's atomic
 // counters leave open) cannot show.  Gated activation: g = min(gate, limit), u = clamp(up, -limit, limit),
-// g * sigmoid(alpha * g) * (u + 1).
+// g * sigmoid(alpha * g) * (u + shift); an infinite limit, alpha = 1 and shift = 0 give silu(gate) * up.
 #include "common.cuh"
 
 namespace {
@@ -71,6 +71,66 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int experts, 
     }
     __syncwarp();
   }
+}
+
+// Router with sigmoid scores and a choice limited to groups of experts: s = sigmoid(logit); the experts form `groups`
+// equal groups of neighbours, a group's score is the sum of its two largest s (of its only one, if it has one expert),
+// only experts of the `keep` best groups (ties: the lower group) can be chosen; the `top` largest s among those (ties:
+// the lower expert); weights = s / (sum of the chosen s + 1e-20) * scale.  One warp per token; logits rows have the
+// stride ld (columns behind `experts` are not the router's).
+__global__ void moe_route_grouped_kernel(const float* __restrict__ logits, int ld, int experts, int top, int groups, int keep,
+                                         float scale, int* __restrict__ choice, float* __restrict__ weight, int n) {
+  extern __shared__ float score_s[];       // [warps][experts + groups]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n) return;
+  float* s = score_s + (long long)warp * (experts + groups);
+  float* gs = s + experts;
+  const float* z = logits + (long long)t * ld;
+  for (int e = lane; e < experts; e += 32) s[e] = 1.f / (1.f + expf(-z[e]));
+  __syncwarp();
+  const int size = experts / groups;
+  for (int g = lane; g < groups; g += 32) {
+    float a = -1.f, b = -1.f;                  // the two largest of the group
+    for (int e = g * size; e < (g + 1) * size; ++e) {
+      const float v = s[e];
+      if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+    }
+    gs[g] = a + (size > 1 ? b : 0.f);
+  }
+  __syncwarp();
+  // strike the groups that are not among the `keep` best: a group is kept if fewer than `keep` groups beat it
+  for (int g = lane; g < groups; g += 32) {
+    int better = 0;
+    for (int o = 0; o < groups; ++o) better += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+    if (better >= keep)
+      for (int e = g * size; e < (g + 1) * size; ++e) s[e] = -2.f;
+  }
+  __syncwarp();
+  float sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int at = experts;
+    for (int e = lane; e < experts; e += 32)
+      if (s[e] > best) { best = s[e]; at = e; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    sum += best;
+    if (lane == 0) {
+      choice[(long long)t * top + k] = at;
+      weight[(long long)t * top + k] = best;
+      s[at] = -2.f;
+    }
+    __syncwarp();
+  }
+  if (lane < top) weight[(long long)t * top + lane] = weight[(long long)t * top + lane] / (sum + 1e-20f) * scale;
+  for (int k = 32 + lane; k < top; k += 32) weight[(long long)t * top + k] = weight[(long long)t * top + k] / (sum + 1e-20f) * scale;
 }
 
 __global__ void __launch_bounds__(PLAN_THREADS)
@@ -158,10 +218,10 @@ moe_gather_rows_kernel(const uint4* __restrict__ x, long long ld_x16, int top, c
   for (int i = threadIdx.x; i < width16; i += 128) dst[i] = src[i];
 }
 
-__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
+__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha, float shift) {
   const float g = fminf(gate, limit);
   const float u = fminf(fmaxf(up, -limit), limit);
-  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+  return g / (1.f + expf(-alpha * g)) * (u + shift);
 }
 
 // One tile: MOE_TILE rows x COLS columns, 256 threads, thread (ty = tid / 16, tx = tid % 16) owns rows ty, ty + 16 and
@@ -171,7 +231,7 @@ __global__ void __launch_bounds__(THREADS)
 moe_expert_kernel(const T* __restrict__ a, long long ld_a, int top, const T* __restrict__ w1, const T* __restrict__ w2,
                   long long expert_stride, int n_out, int k_dim, const int* __restrict__ offsets, const int* __restrict__ sorted,
                   const int* __restrict__ tile_expert, const int* __restrict__ tile_row, T* __restrict__ hidden,
-                  float* __restrict__ pair_out, long long ld_out, float limit, float alpha) {
+                  float* __restrict__ pair_out, long long ld_out, float limit, float alpha, float shift) {
   __shared__ float a_s[MOE_TILE][KSTEP + 1], w1_s[COLS][KSTEP + 1], w2_s[GATED ? COLS : 1][KSTEP + 1];
   __shared__ int row_src[MOE_TILE], row_dst[MOE_TILE];
   pdl_wait();
@@ -234,7 +294,7 @@ moe_expert_kernel(const T* __restrict__ a, long long ld_a, int top, const T* __r
     for (int j = 0; j < 4; ++j) {
       const int c = col0 + tx + 16 * j;
       if (c >= n_out) continue;
-      if constexpr (GATED) hidden[(long long)dst * ld_out + c] = from_f32<T>(clamped_glu(acc1[i][j], acc2[i][j], limit, alpha));
+      if constexpr (GATED) hidden[(long long)dst * ld_out + c] = from_f32<T>(clamped_glu(acc1[i][j], acc2[i][j], limit, alpha, shift));
       else pair_out[(long long)dst * ld_out + c] = acc1[i][j];
     }
   }
@@ -242,12 +302,16 @@ moe_expert_kernel(const T* __restrict__ a, long long ld_a, int top, const T* __r
 
 __global__ void __launch_bounds__(THREADS)
 moe_combine_kernel(const float* __restrict__ pair_out, const float* __restrict__ weight, const int* __restrict__ place, int top,
-                   float* __restrict__ y, int width, int accumulate) {      // place: the row of each pair (null: the pair's index)
+                   float* __restrict__ y, int width, int accumulate,      // place: the row of each pair (null: the pair's index)
+                   const float* __restrict__ extra, const float* __restrict__ extra_gate, long long ld_gate) {
   pdl_wait();
   pdl_launch_dependents();
   const long long t = blockIdx.x;
+  // extra [n, width]: one more term per token (an expert every token uses), times sigmoid(extra_gate[t * ld_gate])
+  const float eg = extra != nullptr ? (extra_gate != nullptr ? 1.f / (1.f + expf(-extra_gate[t * ld_gate])) : 1.f) : 0.f;
   for (int c = threadIdx.x; c < width; c += THREADS) {
     float acc = accumulate ? y[t * width + c] : 0.f;
+    if (extra != nullptr) acc = fmaf(eg, extra[t * width + c], acc);
     for (int k = 0; k < top; ++k) {
       const long long row = place ? place[t * top + k] : t * top + k;
       acc = fmaf(weight[t * top + k], pair_out[row * width + c], acc);
@@ -259,14 +323,14 @@ moe_combine_kernel(const float* __restrict__ pair_out, const float* __restrict__
 template <typename T>
 int launch_experts(bool gated, const void* a, long long ld_a, int top, const void* w1, const void* w2, long long expert_stride,
                    int n_out, int k_dim, const int* offsets, const int* sorted, const int* tile_expert, const int* tile_row,
-                   void* hidden, float* pair_out, long long ld_out, float limit, float alpha, int max_tiles, cudaStream_t stream) {
+                   void* hidden, float* pair_out, long long ld_out, float limit, float alpha, float shift, int max_tiles, cudaStream_t stream) {
   dim3 grid(max_tiles, (n_out + COLS - 1) / COLS);
   if (gated)
     hfee_launch(moe_expert_kernel<T, true>, grid, dim3(THREADS), 0, stream, (const T*)a, ld_a, top, (const T*)w1, (const T*)w2,
-                expert_stride, n_out, k_dim, offsets, sorted, tile_expert, tile_row, (T*)hidden, pair_out, ld_out, limit, alpha);
+                expert_stride, n_out, k_dim, offsets, sorted, tile_expert, tile_row, (T*)hidden, pair_out, ld_out, limit, alpha, shift);
   else
     hfee_launch(moe_expert_kernel<T, false>, grid, dim3(THREADS), 0, stream, (const T*)a, ld_a, top, (const T*)w1, (const T*)w2,
-                expert_stride, n_out, k_dim, offsets, sorted, tile_expert, tile_row, (T*)hidden, pair_out, ld_out, limit, alpha);
+                expert_stride, n_out, k_dim, offsets, sorted, tile_expert, tile_row, (T*)hidden, pair_out, ld_out, limit, alpha, shift);
   return hfee_check_launch(gated ? "moe_gate_up" : "moe_down");
 }
 
@@ -300,16 +364,16 @@ HFEE_API int hfee_moe_plan(const int* choice, int pairs, int experts, int* offse
 // expert_stride: elements from one expert's w_gate (and w_up) to the next one's.
 HFEE_API int hfee_moe_gate_up(const void* x, long long ld_x, int top, const void* w_gate, const void* w_up, long long expert_stride,
                               int inner, int width, const int* offsets, const int* sorted, const int* tile_expert, const int* tile_row, void* hidden,
-                              long long ld_hidden, float limit, float alpha, int max_tiles, int dtype, cudaStream_t stream) {
+                              long long ld_hidden, float limit, float alpha, float shift, int max_tiles, int dtype, cudaStream_t stream) {
   if (max_tiles == 0) return HFEE_OK;
   HFEE_REQUIRE(inner > 0 && width > 0 && top > 0 && ld_x >= width && ld_hidden >= inner && limit > 0.f &&
                expert_stride >= (long long)inner * width, "moe_gate_up: bad sizes");
   if (dtype == HFEE_F32)
     return launch_experts<float>(true, x, ld_x, top, w_gate, w_up, expert_stride, inner, width, offsets, sorted, tile_expert,
-                                 tile_row, hidden, nullptr, ld_hidden, limit, alpha, max_tiles, stream);
+                                 tile_row, hidden, nullptr, ld_hidden, limit, alpha, shift, max_tiles, stream);
   if (dtype == HFEE_BF16)
     return launch_experts<__nv_bfloat16>(true, x, ld_x, top, w_gate, w_up, expert_stride, inner, width, offsets, sorted,
-                                         tile_expert, tile_row, hidden, nullptr, ld_hidden, limit, alpha, max_tiles, stream);
+                                         tile_expert, tile_row, hidden, nullptr, ld_hidden, limit, alpha, shift, max_tiles, stream);
   return hfee_fail(HFEE_ERR_ARG, "moe_gate_up: unknown dtype %d", dtype);
 }
 
@@ -321,19 +385,41 @@ HFEE_API int hfee_moe_down(const void* hidden, long long ld_hidden, int top, con
   HFEE_REQUIRE(inner > 0 && width > 0 && top > 0 && ld_hidden >= inner, "moe_down: bad sizes");
   if (dtype == HFEE_F32)
     return launch_experts<float>(false, hidden, ld_hidden, top, w_down, nullptr, (long long)inner * width, width, inner, offsets, sorted,
-                                 tile_expert, tile_row, nullptr, pair_out, width, 0.f, 0.f, max_tiles, stream);
+                                 tile_expert, tile_row, nullptr, pair_out, width, 0.f, 0.f, 0.f, max_tiles, stream);
   if (dtype == HFEE_BF16)
     return launch_experts<__nv_bfloat16>(false, hidden, ld_hidden, top, w_down, nullptr, (long long)inner * width, width, inner, offsets,
-                                         sorted, tile_expert, tile_row, nullptr, pair_out, width, 0.f, 0.f, max_tiles, stream);
+                                         sorted, tile_expert, tile_row, nullptr, pair_out, width, 0.f, 0.f, 0.f, max_tiles, stream);
   return hfee_fail(HFEE_ERR_ARG, "moe_down: unknown dtype %d", dtype);
+}
+
+HFEE_API int hfee_moe_combine_extra(const float* pair_out, const float* weight, const int* place, int n, int top, float* y, int width,
+                                    int accumulate, const float* extra, const float* extra_gate, long long ld_gate,
+                                    cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(n > 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+  HFEE_REQUIRE(extra != nullptr || extra_gate == nullptr, "moe_combine: a gate without the term it gates");
+  hfee_launch(moe_combine_kernel, dim3(n), dim3(THREADS), 0, stream, pair_out, weight, place, top, y, width, accumulate, extra,
+              extra_gate, ld_gate);
+  return hfee_check_launch("moe_combine");
 }
 
 HFEE_API int hfee_moe_combine(const float* pair_out, const float* weight, const int* place, int n, int top, float* y, int width,
                               int accumulate, cudaStream_t stream) {
+  return hfee_moe_combine_extra(pair_out, weight, place, n, top, y, width, accumulate, nullptr, nullptr, 0, stream);
+}
+
+// logits: [n, ld] float32 of which the first `experts` columns are the router's.
+HFEE_API int hfee_moe_route_grouped(const float* logits, long long ld, int n, int experts, int top, int groups, int keep, float scale,
+                                    int* choice, float* weight, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
-  HFEE_REQUIRE(n > 0 && top > 0 && width > 0, "moe_combine: bad sizes");
-  hfee_launch(moe_combine_kernel, dim3(n), dim3(THREADS), 0, stream, pair_out, weight, place, top, y, width, accumulate);
-  return hfee_check_launch("moe_combine");
+  HFEE_REQUIRE(experts >= 1 && experts <= MAX_EXPERTS && groups >= 1 && experts % groups == 0 && keep >= 1 && keep <= groups,
+               "moe_route_grouped: %d experts in %d groups of which %d are kept", experts, groups, keep);
+  HFEE_REQUIRE(top >= 1 && top <= keep * (experts / groups), "moe_route_grouped: top %d exceeds the experts of the kept groups", top);
+  HFEE_REQUIRE(ld >= experts, "moe_route_grouped: ld is too small");
+  const int warps = 4;
+  hfee_launch(moe_route_grouped_kernel, dim3((n + warps - 1) / warps), dim3(warps * 32), (size_t)warps * (experts + groups) * sizeof(float),
+              stream, logits, (int)ld, experts, top, groups, keep, scale, choice, weight, n);
+  return hfee_check_launch("moe_route_grouped");
 }
 
 // place_of_pair: [pairs]; row_pair: [max_tiles * tile_rows]; tile_group: [max_tiles], max_tiles >= pairs / tile_rows +

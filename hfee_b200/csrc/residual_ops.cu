@@ -49,23 +49,23 @@ softcap_kernel(float* __restrict__ x, long long ld, int cols, float cap) {
   for (int c = c0 + threadIdx.x; c < c1; c += ROW_THREADS) row[c] = cap * tanhf(row[c] * inv);
 }
 
-__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
+__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha, float shift) {
   const float g = fminf(gate, limit);
   const float u = fminf(fmaxf(up, -limit), limit);
-  return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+  return g / (1.f + expf(-alpha * g)) * (u + shift);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
 clamped_glu_kernel(const T* __restrict__ gate_up, long long ld_in, T* __restrict__ out, long long ld_out, int inner,
-                   int granule, float limit, float alpha) {
+                   int granule, float limit, float alpha, float shift) {
   pdl_wait();
   pdl_launch_dependents();
   const T* in = gate_up + (long long)blockIdx.x * ld_in;
   T* o = out + (long long)blockIdx.x * ld_out;
   for (int c = threadIdx.x; c < inner; c += ROW_THREADS) {
     const int at = (c / granule) * 2 * granule + c % granule;
-    o[c] = from_f32<T>(clamped_glu(to_f32<T>(in[at]), to_f32<T>(in[at + granule]), limit, alpha));
+    o[c] = from_f32<T>(clamped_glu(to_f32<T>(in[at]), to_f32<T>(in[at + granule]), limit, alpha, shift));
   }
 }
 
@@ -139,16 +139,16 @@ HFEE_API int hfee_softcap(float* x, long long ld, int rows, int cols, float cap,
 }
 
 HFEE_API int hfee_clamped_glu(const void* gate_up, long long ld_in, void* out, long long ld_out, int n, int inner, int granule,
-                              float limit, float alpha, int dtype, cudaStream_t stream) {
+                              float limit, float alpha, float shift, int dtype, cudaStream_t stream) {
   if (n == 0) return HFEE_OK;
   HFEE_REQUIRE(n > 0 && inner > 0 && granule > 0 && inner % granule == 0, "clamped_glu: inner %d is not a multiple of the granule %d", inner, granule);
   HFEE_REQUIRE(ld_in >= 2 * inner && ld_out >= inner && limit > 0.f, "clamped_glu: a row stride is too small or the limit is not positive");
   if (dtype == HFEE_F32)
     hfee_launch(clamped_glu_kernel<float>, dim3(n), dim3(ROW_THREADS), 0, stream, (const float*)gate_up, ld_in, (float*)out, ld_out,
-                inner, granule, limit, alpha);
+                inner, granule, limit, alpha, shift);
   else if (dtype == HFEE_BF16)
     hfee_launch(clamped_glu_kernel<__nv_bfloat16>, dim3(n), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)gate_up, ld_in,
-                (__nv_bfloat16*)out, ld_out, inner, granule, limit, alpha);
+                (__nv_bfloat16*)out, ld_out, inner, granule, limit, alpha, shift);
   else
     return hfee_fail(HFEE_ERR_ARG, "clamped_glu: unknown dtype %d", dtype);
   return hfee_check_launch("clamped_glu");

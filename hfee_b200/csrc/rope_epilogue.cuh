@@ -20,9 +20,9 @@ struct RopeEpi {
   __nv_bfloat16* k_pool; __nv_bfloat16* v_pool;      // null: every head is a query head
   PagedCache cache;
   int heads, kv_heads, head_dim, interleaved;
-  // The struct also carries the two numbers of the clamped gated epilogue (out = g sigmoid(alpha g) (u + 1) with
+  // The struct also carries the three numbers of the clamped gated epilogue (out = g sigmoid(alpha g) (u + shift) with
   // g = min(gate, limit), u = clamp(up, -limit, limit)) to the kernels; the rotary epilogue does not read them.
-  float act_limit, act_alpha;
+  float act_limit, act_alpha, act_shift;
 };
 
 // One epilogue warp's share of a tile of BN columns that starts at column n0: `tmem_rows` is the

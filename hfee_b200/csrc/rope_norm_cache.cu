@@ -11,6 +11,12 @@
 //                               RMS-normed with its weight into a buffer, the key/value latent RMS-normed
 //                               with its weight into the leading dimensions of the token's cached vector,
 //                               the rotated tail behind it.
+//   hfee_attention_prepare     one token's [q | k | v] projection on its way to the score kernel: a bias per column
+//                               (each optional), an RMS norm with a weight over the whole query and the whole key
+//                               projection (all heads at once; optional), then the rotation of the first `rope_dim`
+//                               dimensions of every query and key head, pairing dimension i with i + rope_dim/2 or
+//                               2i with 2i + 1; queries to a buffer, keys and values to their cache pages.  Key and
+//                               value sizes are independent.  One block per token, the row in shared memory.
 #include "common.cuh"
 
 namespace {
@@ -140,6 +146,94 @@ latent_norm_rope_cache_kernel(const T* __restrict__ proj, long long ld, int q_of
   }
 }
 
+
+constexpr int AP_THREADS = 128;
+
+__device__ __forceinline__ float block_sum_ap(float v, float* partial) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < AP_THREADS / 32; ++i) total += partial[i];
+  return total;
+}
+
+// element d of a head of `len` dimensions in shared memory after the rotation
+__device__ __forceinline__ float rotated_s(const float* __restrict__ x, int d, int rope_dim, int interleaved,
+                                           const float* __restrict__ cs) {
+  const float v = x[d];
+  if (cs == nullptr || d >= rope_dim) return v;
+  if (interleaved) {
+    const int i = d >> 1;
+    return (d & 1) ? v * cs[2 * i] + x[d - 1] * cs[2 * i + 1] : v * cs[2 * i] - x[d + 1] * cs[2 * i + 1];
+  }
+  const int half = rope_dim >> 1;
+  if (d < half) return v * cs[2 * d] - x[d + half] * cs[2 * d + 1];
+  return v * cs[2 * (d - half)] + x[d - half] * cs[2 * (d - half) + 1];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(AP_THREADS)
+attention_prepare_kernel(const T* __restrict__ src, long long ld_src, int q_off, int k_off, int v_off,
+                         const float* __restrict__ bq, const float* __restrict__ bk, const float* __restrict__ bv,
+                         const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                         const float* __restrict__ cs, int rope_dim, int interleaved,
+                         const int* __restrict__ positions, const int* __restrict__ slot_of_token,
+                         T* __restrict__ q_out, long long ld_q, T* __restrict__ k_pool, PagedCache kc,
+                         T* __restrict__ v_pool, PagedCache vc, int heads, int key_dim) {
+  extern __shared__ float row_s[];            // [q_cols | k_cols | v_cols]
+  __shared__ float partial[AP_THREADS / 32];
+  const int i = blockIdx.x;
+  const int pos = positions[i], slot = slot_of_token[i];
+  pdl_wait();
+  pdl_launch_dependents();
+  const bool write = k_pool != nullptr;
+  const int q_cols = heads * key_dim, k_cols = write ? kc.kv_heads * key_dim : 0, v_cols = write ? vc.kv_heads * vc.head_dim : 0;
+  const T* row = src + (long long)i * ld_src;
+  float* qs = row_s;
+  float* ks = qs + q_cols;
+  float* vs = ks + k_cols;
+  float ssq = 0.f, ssk = 0.f;
+  for (int c = threadIdx.x; c < q_cols; c += AP_THREADS) {
+    const float v = to_f32<T>(row[q_off + c]) + (bq != nullptr ? bq[c] : 0.f);
+    qs[c] = v;
+    ssq = fmaf(v, v, ssq);
+  }
+  for (int c = threadIdx.x; c < k_cols; c += AP_THREADS) {
+    const float v = to_f32<T>(row[k_off + c]) + (bk != nullptr ? bk[c] : 0.f);
+    ks[c] = v;
+    ssk = fmaf(v, v, ssk);
+  }
+  for (int c = threadIdx.x; c < v_cols; c += AP_THREADS) vs[c] = to_f32<T>(row[v_off + c]) + (bv != nullptr ? bv[c] : 0.f);
+  if (wq != nullptr) {
+    const float scale = 1.0f / sqrtf(block_sum_ap(ssq, partial) / (float)q_cols + eps);
+    for (int c = threadIdx.x; c < q_cols; c += AP_THREADS) qs[c] = qs[c] * scale * wq[c];      // a thread's own columns
+  }
+  if (wk != nullptr && write) {
+    const float scale = 1.0f / sqrtf(block_sum_ap(ssk, partial) / (float)k_cols + eps);
+    for (int c = threadIdx.x; c < k_cols; c += AP_THREADS) ks[c] = ks[c] * scale * wk[c];
+  }
+  __syncthreads();
+  const float* csr = cs != nullptr ? cs + (long long)i * rope_dim : nullptr;
+  T* qrow = q_out + (long long)i * ld_q;
+  for (int c = threadIdx.x; c < q_cols; c += AP_THREADS) {
+    const int h = c / key_dim, d = c - h * key_dim;
+    qrow[c] = from_f32<T>(rotated_s(qs + h * key_dim, d, rope_dim, interleaved, csr));
+  }
+  if (!write) return;
+  for (int c = threadIdx.x; c < k_cols; c += AP_THREADS) {
+    const int g = c / key_dim, d = c - g * key_dim;
+    k_pool[paged_offset(kc, slot, pos, g) + d] = from_f32<T>(rotated_s(ks + g * key_dim, d, rope_dim, interleaved, csr));
+  }
+  const int vd = vc.head_dim;
+  for (int c = threadIdx.x; c < v_cols; c += AP_THREADS) {
+    const int g = c / vd, d = c - g * vd;
+    v_pool[paged_offset(vc, slot, pos, g) + d] = from_f32<T>(vs[c]);
+  }
+}
+
 template <typename T>
 int launch_rope_norm(const void* src, long long ld_src, int n, const float* cs, int rope_dim, float norm_eps,
                      const int* positions, const int* slot_of_token, const HeadGroup& qg, void* q_out, long long ld_q,
@@ -202,6 +296,42 @@ HFEE_API int hfee_rope_norm_cache(const void* src, long long ld_src, int dtype, 
   if (dtype == HFEE_BF16)
     return launch_rope_norm<__nv_bfloat16>(src, ld_src, n, cs, rope_dim, norm_eps, positions, slot_of_token, qg, q_out, ld_q, kg, k_pool, kc, vg, v_pool, vc, stream);
   return hfee_fail(HFEE_ERR_ARG, "rope_norm_cache: unknown dtype %d", dtype);
+}
+
+// src rows hold the query projection at q_off (heads * key_dim columns), the key projection at k_off (kv_heads *
+// key_dim) and the value projection at v_off (kv_heads * value_dim).  bq, bk, bv: a bias per column (float32, each may
+// be null); wq, wk: weights of an RMS norm over the whole query / key projection (null: no norm); cs: [n, rope_dim/2,
+// 2] cosines and sines (null: no rotation); interleaved: pairs (2i, 2i+1) instead of (i, i + rope_dim/2).  k_pool null:
+// queries only (a run that reads a cache another run filled).
+HFEE_API int hfee_attention_prepare(const void* src, long long ld_src, int dtype, int n, int q_off, int k_off, int v_off,
+                                    const float* bq, const float* bk, const float* bv, const float* wq, const float* wk,
+                                    float eps, const float* cs, int rope_dim, int interleaved, const int* positions,
+                                    const int* slot_of_token, void* q_out, long long ld_q, void* k_pool, void* v_pool,
+                                    const int* block_table, int max_pages, int page_size, int heads, int kv_heads,
+                                    int key_dim, int value_dim, cudaStream_t stream) {
+  if (n == 0) return HFEE_OK;
+  HFEE_REQUIRE(heads > 0 && kv_heads > 0 && key_dim > 0 && value_dim > 0, "attention_prepare: bad sizes");
+  HFEE_REQUIRE(rope_dim >= 0 && rope_dim % 2 == 0 && rope_dim <= key_dim,
+               "attention_prepare: rope_dim %d must be even and at most the key size %d", rope_dim, key_dim);
+  HFEE_REQUIRE((k_pool == nullptr) == (v_pool == nullptr), "attention_prepare: keys and values are cached together");
+  HFEE_REQUIRE(ld_q >= (long long)heads * key_dim, "attention_prepare: ld_q is too small");
+  PagedCache kc{}, vc{};
+  HFEE_REQUIRE(make_paged_cache(&kc, block_table, max_pages, page_size, kv_heads, key_dim), "page_size %d must be a power of two", page_size);
+  make_paged_cache(&vc, block_table, max_pages, page_size, kv_heads, value_dim);
+  const size_t smem = sizeof(float) * ((size_t)heads * key_dim + (k_pool != nullptr ? (size_t)kv_heads * (key_dim + value_dim) : 0));
+  HFEE_REQUIRE(smem <= 48 * 1024, "attention_prepare: a token's projections (%zu bytes as float32) exceed 48 KB", smem);
+  if (cs == nullptr) rope_dim = 0;
+  if (dtype == HFEE_F32)
+    hfee_launch(attention_prepare_kernel<float>, dim3(n), dim3(AP_THREADS), smem, stream, (const float*)src, ld_src, q_off, k_off, v_off,
+                bq, bk, bv, wq, wk, eps, cs, rope_dim, interleaved, positions, slot_of_token, (float*)q_out, ld_q, (float*)k_pool, kc,
+                (float*)v_pool, vc, heads, key_dim);
+  else if (dtype == HFEE_BF16)
+    hfee_launch(attention_prepare_kernel<__nv_bfloat16>, dim3(n), dim3(AP_THREADS), smem, stream, (const __nv_bfloat16*)src, ld_src,
+                q_off, k_off, v_off, bq, bk, bv, wq, wk, eps, cs, rope_dim, interleaved, positions, slot_of_token,
+                (__nv_bfloat16*)q_out, ld_q, (__nv_bfloat16*)k_pool, kc, (__nv_bfloat16*)v_pool, vc, heads, key_dim);
+  else
+    return hfee_fail(HFEE_ERR_ARG, "attention_prepare: unknown dtype %d", dtype);
+  return hfee_check_launch("attention_prepare");
 }
 
 // proj rows hold the query latent at q_off (q_rank columns) and [key/value latent | tail to rotate] at kv_off

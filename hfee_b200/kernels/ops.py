@@ -77,20 +77,34 @@ _SIGNATURES = {
     "hfee_attention_mma_distance_tile": [_I, _I],
     "hfee_add_sinusoid": [_P, _P, _I, _I, _F, _P],
     "hfee_softcap": [_P, _L, _I, _I, _F, _P],
-    "hfee_clamped_glu": [_P, _L, _P, _L, _I, _I, _I, _F, _F, _I, _P],
+    "hfee_clamped_glu": [_P, _L, _P, _L, _I, _I, _I, _F, _F, _F, _I, _P],
     "hfee_scaled_add_norm": [_P, _F, _P, _P, _F, _P, _L, _I, _I, _I, _P],
     "hfee_depth_average": [_P, _P, _F, _P, _L, _P, _I, _I, _I, _P],
     "hfee_mingru": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
     "hfee_selective_scan": [_P, _L, _P, _L, _P, _L, _I, _I, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _F, _I, _I, _P],
     "hfee_moe_route": [_P, _I, _I, _I, _F, _P, _P, _P],
     "hfee_moe_plan": [_P, _I, _I, _P, _P, _P, _P, _I, _P],
-    "hfee_moe_gate_up": [_P, _L, _I, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _L, _F, _F, _I, _I, _P],
+    "hfee_moe_gate_up": [_P, _L, _I, _P, _P, _L, _I, _I, _P, _P, _P, _P, _P, _L, _F, _F, _F, _I, _I, _P],
     "hfee_moe_down": [_P, _L, _I, _P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _P],
     "hfee_moe_combine": [_P, _P, _P, _I, _I, _P, _I, _I, _P],
     "hfee_moe_plan_tiles": [_P, _I, _I, _I, _P, _P, _P, _I, _P],
     "hfee_moe_gather_rows": [_P, _L, _I, _P, _P, _I, _P, _L, _I, _I, _P],
-    "hfee_gemm_tcgen05_grouped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _I, _F, _F, _P, _P],
-    "hfee_gemm_tcgen05_pair_clamped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _F, _F, _P, _P],
+    "hfee_gemm_tcgen05_grouped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P, _I, _F, _F, _F, _P, _P],
+    "hfee_gemm_tcgen05_pair_clamped": [_P, _L, _P, _L, _P, _L, _I, _I, _I, _F, _F, _F, _P, _P],
+    "hfee_embed_bigram": [_P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _P],
+    "hfee_remember_tokens": [_P, _P, _P, _P, _P, _I, _P, _P],
+    "hfee_layernorm": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _F, _P],
+    "hfee_add_bias": [_P, _L, _P, _I, _I, _P],
+    "hfee_attention_prepare": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _F, _P, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I,
+                               _I, _I, _I, _I, _P],
+    "hfee_attention_simt_sink": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _P, _P, _L, _I,
+                                 _P, _P, _F, _P, _I, _P],
+    "hfee_attention_mma_general": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _F, _I,
+                                   _I, _P, _P],
+    "hfee_gated_recurrence": [_I, _P, _P, _P, _L, _I, _P, _L, _P, _F, _F, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
+    "hfee_head_norm_gate_scaled": [_P, _L, _P, _I, _F, _P, _L, _P, _L, _I, _I, _I, _I, _F, _I, _P],
+    "hfee_moe_combine_extra": [_P, _P, _P, _I, _I, _P, _I, _I, _P, _P, _L, _P],
+    "hfee_moe_route_grouped": [_P, _L, _I, _I, _I, _I, _I, _F, _P, _P, _P],
     "hfee_conv_act_launches": [_I, _I, _I],
     "hfee_delta_rule": [_P, _L, _I, _I, _I, _P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _P, _L, _P],
     "hfee_head_norm_gate": [_P, _L, _P, _F, _P, _L, _P, _L, _I, _I, _I, _I, _I, _P],
@@ -1365,14 +1379,14 @@ CLAMPED_SWISH_ALPHA = 1.702
 
 
 def clamped_glu(gate_up: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = CLAMPED_SWISH_ALPHA,
-                granule: Optional[int] = None) -> None:
-    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); column layout
-    of :func:`swiglu`."""
+                granule: Optional[int] = None, shift: float = 1.0) -> None:
+    """out = g * sigmoid(alpha * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit); column layout
+    of :func:`swiglu`.  An infinite limit, alpha = 1 and shift = 0 give silu(gate) * up."""
     lib = library()
     n, inner = out.shape
     assert gate_up.shape[1] == 2 * inner and gate_up.dtype == out.dtype
     _check(lib.hfee_clamped_glu(gate_up.data_ptr(), _rows(gate_up, "gate_up"), out.data_ptr(), _rows(out, "out"), n, inner,
-                                int(granule or inner), float(limit), float(alpha), _dt(out), _stream()), lib)
+                                int(granule or inner), float(limit), float(alpha), float(shift), _dt(out), _stream()), lib)
 
 
 def scaled_add_norm(y: torch.Tensor, m: float, residual: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -1463,6 +1477,21 @@ def moe_route(logits: torch.Tensor, top: int, scale: float, choice: torch.Tensor
     _check(lib.hfee_moe_route(logits.data_ptr(), n, experts, top, float(scale), choice.data_ptr(), weight.data_ptr(), _stream()), lib)
 
 
+def moe_route_grouped(logits: torch.Tensor, experts: int, top: int, groups: int, keep: int, scale: float, choice: torch.Tensor,
+                      weight: torch.Tensor) -> None:
+    """Per row of ``logits`` (float32; the first ``experts`` columns): scores sigmoid(logit); the experts form ``groups``
+    equal groups of neighbours, a group's score is the sum of its two largest scores, and only experts of the ``keep`` best
+    groups can be chosen; the ``top`` largest of those (ties: the lower expert) into ``choice`` [n, top] int32, their
+    scores divided by their sum and times ``scale`` into ``weight`` [n, top] float32."""
+    lib = library()
+    n = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= experts and weight.dtype == torch.float32
+    _i32(choice, "choice")
+    assert tuple(choice.shape) == (n, top) and tuple(weight.shape) == (n, top) and weight.is_contiguous()
+    _check(lib.hfee_moe_route_grouped(logits.data_ptr(), logits.stride(0), n, experts, top, groups, keep, float(scale),
+                                      choice.data_ptr(), weight.data_ptr(), _stream()), lib)
+
+
 def moe_plan(choice: torch.Tensor, experts: int, offsets: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor,
              tile_row: torch.Tensor) -> None:
     """Order the (token, choice) pairs by expert: ``offsets`` [experts + 1], ``order`` [pairs] (pair index at each
@@ -1478,7 +1507,7 @@ def moe_plan(choice: torch.Tensor, experts: int, offsets: torch.Tensor, order: t
 
 def moe_experts(x: torch.Tensor, top: int, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, limit: float,
                 offsets: torch.Tensor, order: torch.Tensor, tile_expert: torch.Tensor, tile_row: torch.Tensor,
-                hidden: torch.Tensor, pair_out: torch.Tensor, alpha: float = CLAMPED_SWISH_ALPHA) -> None:
+                hidden: torch.Tensor, pair_out: torch.Tensor, alpha: float = CLAMPED_SWISH_ALPHA, shift: float = 1.0) -> None:
     """For every (token, chosen expert e) pair: pair_out[pair] = W_down[e] act(W_gate[e] x, W_up[e] x) (float32), with the
     clamped gated activation of :func:`clamped_glu`.  ``w_gate``, ``w_up``: [experts, inner, width]; ``w_down``:
     [experts, width, inner]; ``hidden`` [pairs, inner] is scratch in the activations' dtype."""
@@ -1496,16 +1525,18 @@ def moe_experts(x: torch.Tensor, top: int, w_gate: torch.Tensor, w_up: torch.Ten
     _check(lib.hfee_moe_gate_up(x.data_ptr(), _rows(x, "x"), top, w_gate.data_ptr(), w_up.data_ptr(), w_gate.stride(0), inner, width,
                                 offsets.data_ptr(),
                                 order.data_ptr(), tile_expert.data_ptr(), tile_row.data_ptr(), hidden.data_ptr(),
-                                _rows(hidden, "hidden"), float(limit), float(alpha), tiles, _dt(x), _stream()), lib)
+                                _rows(hidden, "hidden"), float(limit), float(alpha), float(shift), tiles, _dt(x), _stream()), lib)
     _check(lib.hfee_moe_down(hidden.data_ptr(), _rows(hidden, "hidden"), top, w_down.data_ptr(), inner, width, offsets.data_ptr(),
                              order.data_ptr(), tile_expert.data_ptr(), tile_row.data_ptr(), pair_out.data_ptr(), tiles, _dt(x),
                              _stream()), lib)
 
 
 def moe_combine(pair_out: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, accumulate: bool,
-                place: Optional[torch.Tensor] = None) -> None:
+                place: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
+                extra_gate: Optional[torch.Tensor] = None) -> None:
     """y[t] (+)= sum_k weight[t, k] * pair_out[row of pair t * top + k] (float32); the row is ``place[pair]``, or the
-    pair's index without ``place``."""
+    pair's index without ``place``.  ``extra`` [n, width] float32 is one more term per token, times
+    ``sigmoid(extra_gate[t])`` when ``extra_gate`` (a float32 column, any row stride) is given."""
     lib = library()
     n, top = weight.shape
     assert y.dtype == torch.float32 and y.is_contiguous() and y.shape[0] == n and pair_out.shape[1] == y.shape[1]
@@ -1513,8 +1544,13 @@ def moe_combine(pair_out: torch.Tensor, weight: torch.Tensor, y: torch.Tensor, a
     if place is not None:
         _i32(place, "place")
         assert place.numel() >= n * top
-    _check(lib.hfee_moe_combine(pair_out.data_ptr(), weight.data_ptr(), _ptr(place), n, top, y.data_ptr(), y.shape[1], int(accumulate),
-                                _stream()), lib)
+    if extra is not None:
+        assert extra.dtype == torch.float32 and extra.is_contiguous() and tuple(extra.shape) == tuple(y.shape)
+    if extra_gate is not None:
+        assert extra is not None and extra_gate.dtype == torch.float32 and extra_gate.shape[0] == n
+    _check(lib.hfee_moe_combine_extra(pair_out.data_ptr(), weight.data_ptr(), _ptr(place), n, top, y.data_ptr(), y.shape[1],
+                                      int(accumulate), _ptr(extra), _ptr(extra_gate),
+                                      extra_gate.stride(0) if extra_gate is not None else 0, _stream()), lib)
 
 
 GROUPED_TILE_ROWS = 128         # rows of a tile of the grouped product
@@ -1547,10 +1583,10 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Ten
     assert w.shape[2] == k and w.is_contiguous() and a.dtype == w.dtype == torch.bfloat16
     assert m % GROUPED_TILE_ROWS == 0 and tile_group.numel() >= m // GROUPED_TILE_ROWS
     assert tuple(out.shape) == (m, n // 2 if clamped else n)
-    limit, alpha = clamped or (0.0, 0.0)
+    limit, alpha, shift = (tuple(clamped) + (1.0,))[:3] if clamped else (0.0, 0.0, 0.0)
     _check(lib.hfee_gemm_tcgen05_grouped(a.data_ptr(), _rows(a, "gemm a"), w.data_ptr(), k, out.data_ptr(), _rows(out, "gemm out"),
                                          _dt(out), m, n, k, groups, tile_group.data_ptr(), int(clamped is not None), float(limit),
-                                         float(alpha), _status().data_ptr(), _stream()), lib)
+                                         float(alpha), float(shift), _status().data_ptr(), _stream()), lib)
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, granule: int = 4) -> torch.Tensor:
@@ -1566,7 +1602,7 @@ CLAMPED_PAIR_MIN_TOKENS = 65
 
 
 def linear_clamped_glu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor, granule: int, scratch: torch.Tensor,
-                       limit: float, alpha: float = 1.702) -> None:
+                       limit: float, alpha: float = 1.702, shift: float = 1.0) -> None:
     """out = :func:`clamped_glu` of ``a @ w_gate_up^T`` (rows of ``w_gate_up`` in runs of ``granule`` gate and ``granule`` up
     rows): in the epilogue of the paired tcgen05 product for prompt portions in bfloat16, else through ``scratch``
     [m, 2 * inner]."""
@@ -1577,16 +1613,16 @@ def linear_clamped_glu(a: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tens
         lib = library()
         _check(lib.hfee_gemm_tcgen05_pair_clamped(a.data_ptr(), _rows(a, "gemm a"), w_gate_up.data_ptr(), _rows(w_gate_up, "gemm w"),
                                                   out.data_ptr(), _rows(out, "gemm out"), m, n, k, float(limit), float(alpha),
-                                                  _status().data_ptr(), _stream()), lib)
+                                                  float(shift), _status().data_ptr(), _stream()), lib)
         return
     linear(a, w_gate_up, scratch)
-    clamped_glu(scratch, out, limit, alpha, granule)
+    clamped_glu(scratch, out, limit, alpha, granule, shift)
 
 
 def moe_experts_grouped(x: torch.Tensor, top: int, choice: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, limit: float,
                         place: torch.Tensor, row_pair: torch.Tensor, tile_group: torch.Tensor, rows_in: torch.Tensor,
                         gate_up: torch.Tensor, hidden: torch.Tensor, rows_out: torch.Tensor,
-                        alpha: float = CLAMPED_SWISH_ALPHA) -> None:
+                        alpha: float = CLAMPED_SWISH_ALPHA, shift: float = 1.0) -> None:
     """The experts' two products on the tensor cores: rows_out[place[pair]] = W_down[e] act(W_gate[e] x, W_up[e] x) for every
     (token, chosen expert e) pair, float32.  ``w_gate_up`` [experts, 2 * inner, width] holds each expert's gate rows, then
     its up rows; ``w_down`` [experts, width, inner].  Scratch, all of ``tiles * 128`` rows with ``tiles =
@@ -1609,10 +1645,10 @@ def moe_experts_grouped(x: torch.Tensor, top: int, choice: torch.Tensor, w_gate_
     _check(lib.hfee_moe_gather_rows(x.data_ptr(), _rows(x, "x"), top, row_pair.data_ptr(), tile_group.data_ptr(), GROUPED_TILE_ROWS,
                                     rows_in.data_ptr(), _rows(rows_in, "rows_in"), width, tiles, _stream()), lib)
     if gate_up is None:         # the activation in the first product's epilogue
-        gemm_tcgen05_grouped(rows_in[:rows], w_gate_up, tile_group, hidden[:rows], clamped=(limit, alpha))
+        gemm_tcgen05_grouped(rows_in[:rows], w_gate_up, tile_group, hidden[:rows], clamped=(limit, alpha, shift))
     else:
         gemm_tcgen05_grouped(rows_in[:rows], w_gate_up, tile_group, gate_up[:rows])
-        clamped_glu(gate_up[:rows], hidden[:rows], limit, alpha)
+        clamped_glu(gate_up[:rows], hidden[:rows], limit, alpha, shift=shift)
     gemm_tcgen05_grouped(hidden[:rows], w_down, tile_group, rows_out[:rows])
 
 
@@ -1641,6 +1677,159 @@ def qk_norm_rope_cache(qk: torch.Tensor, q_weight: Optional[torch.Tensor], k_wei
                                        q_out.data_ptr(), _rows(q_out, "q_out"), _ptr(k_pool), _ptr(v_pool),
                                        block_table.data_ptr(), block_table.shape[1], page_size, n, heads, kv_heads,
                                        head_dim, int(v_offset), _dt(qk), _stream()), lib)
+
+
+# ---------------------------------------------------------------------------- bigram embedding, layer norm, biases
+def embed_bigram(table: torch.Tensor, pairs: torch.Tensor, step, last_token: torch.Tensor, out: torch.Tensor, buckets: int,
+                 mul_prev: int, mul_cur: int) -> None:
+    """out[i] = table[token_i] + pairs[(previous token * mul_prev + token_i * mul_cur) mod buckets] as float32; a request's
+    first token takes row ``buckets``.  The token in front of a portion's first token is ``last_token[slot]`` (int32 per
+    request slot), which is then set to the last token each request brought in this step."""
+    lib = library()
+    n, width = out.shape
+    feedback = getattr(step, "feedback", None)
+    _i32(step.token_ids, "tokens"); _i32(last_token, "last_token"); _i32(feedback, "feedback")
+    assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous() and pairs.is_contiguous()
+    assert table.dtype == pairs.dtype and tuple(pairs.shape) == (buckets + 1, width) and table.shape[1] == width
+    _check(lib.hfee_embed_bigram(table.data_ptr(), pairs.data_ptr(), _dt(table), step.token_ids.data_ptr(), step.positions.data_ptr(),
+                                 step.slot_of_token.data_ptr(), _ptr(feedback), last_token.data_ptr(), out.data_ptr(), n, width,
+                                 table.shape[0], int(buckets), int(mul_prev), int(mul_cur), _stream()), lib)
+    _check(lib.hfee_remember_tokens(step.token_ids.data_ptr(), step.slot_of_token.data_ptr(), _ptr(feedback),
+                                    step.cu_tokens.data_ptr(), step.slots.data_ptr(), step.r, last_token.data_ptr(), _stream()), lib)
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None,
+              residual_add: Optional[torch.Tensor] = None) -> None:
+    """out[r] = (x[rows[r] or r] - mean) / sqrt(variance + eps) * weight in float32 arithmetic (no bias).  With
+    ``residual_add`` (float32, like ``x``) the row is ``x + residual_add`` and that sum is stored back to ``x``."""
+    lib = library()
+    _i32(rows, "layernorm rows")
+    assert x.dtype == torch.float32 and x.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == x.shape[1]
+    assert residual_add is None or (residual_add.dtype == torch.float32 and residual_add.is_contiguous()
+                                    and residual_add.shape == x.shape and rows is None)
+    n, width = out.shape
+    _check(lib.hfee_layernorm(x.data_ptr(), _ptr(residual_add), weight.data_ptr(), _ptr(rows), out.data_ptr(), _rows(out, "out"),
+                              _dt(out), n, width, float(eps), _stream()), lib)
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    """x[r, c] += bias[c] (float32)."""
+    lib = library()
+    assert x.dtype == torch.float32 and bias.dtype == torch.float32 and bias.numel() == x.shape[1]
+    _check(lib.hfee_add_bias(x.data_ptr(), _rows(x, "x"), bias.data_ptr(), x.shape[0], x.shape[1], _stream()), lib)
+
+
+def attention_prepare(src: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, key_dim: int,
+                      value_dim: int, step, q_out: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                      block_table: torch.Tensor, page_size: int, cs: Optional[torch.Tensor] = None, rope_dim: int = 0,
+                      interleaved: bool = False, biases=(None, None, None), norm_weights=(None, None), eps: float = 0.0) -> None:
+    """One token's [q | k | v] projection on its way to the score kernel: ``biases`` = (q, k, v) float32 per column (each may
+    be None), ``norm_weights`` = (q, k) weights of an RMS norm over the whole query / key projection (None: no norm),
+    then the rotation of the first ``rope_dim`` dimensions of every head by the step's (cos, sin) table ``cs``, pairing
+    (i, i + rope_dim/2) or, ``interleaved``, (2i, 2i + 1).  Queries to ``q_out``, keys and values to their pages (pools None:
+    queries only)."""
+    lib = library()
+    n = src.shape[0]
+    _i32(block_table, "block_table")
+    for t in biases + norm_weights:
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    assert cs is None or (cs.dtype == torch.float32 and cs.is_contiguous() and cs.numel() == n * rope_dim)
+    assert q_out.dtype == src.dtype and q_out.shape[1] == heads * key_dim
+    if k_pool is not None:
+        assert k_pool.dtype == v_pool.dtype == src.dtype and k_pool.is_contiguous() and v_pool.is_contiguous()
+        assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, key_dim) and tuple(v_pool.shape[1:]) == (kv_heads, page_size, value_dim)
+    _check(lib.hfee_attention_prepare(src.data_ptr(), _rows(src, "src"), _dt(src), n, q_off, k_off, v_off, _ptr(biases[0]),
+                                      _ptr(biases[1]), _ptr(biases[2]), _ptr(norm_weights[0]), _ptr(norm_weights[1]), float(eps),
+                                      _ptr(cs), int(rope_dim) if cs is not None else 0, int(interleaved), step.positions.data_ptr(),
+                                      step.slot_of_token.data_ptr(), q_out.data_ptr(), _rows(q_out, "q_out"), _ptr(k_pool),
+                                      _ptr(v_pool), block_table.data_ptr(), block_table.shape[1], page_size, heads, kv_heads,
+                                      key_dim, value_dim, _stream()), lib)
+
+
+SOFTMAX_ATTENTION_ON_TENSOR_CORES = True
+
+
+def softmax_attention(q, k_pool, v_pool, block_table, page_size, step, out, heads, kv_heads, head_dim, value_dim, scale,
+                      window=0, sink=None, out_scale=1.0, scratch=None) -> None:
+    """Causal grouped-query softmax attention over the paged cache with key and value sizes of their own, an optional
+    window, an optional ``sink`` (float32 per query head: the denominator also holds exp(sink[h]), a term without key or
+    value) and the output times ``out_scale``.  bfloat16 with key and value sizes that are multiples of 8 (up to 256) runs
+    on the tensor cores (prompt portions, decode steps with their keys split among CTAs when ``scratch`` is given, and
+    mixtures), everything else on the CUDA cores in float32 arithmetic."""
+    lib = library()
+    group = heads // kv_heads
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == heads)
+    assert q.shape[1] == heads * head_dim and tuple(out.shape) == (step.n, heads * value_dim) and q.dtype == k_pool.dtype == out.dtype
+    assert k_pool.is_contiguous() and v_pool.is_contiguous() and v_pool.dtype == q.dtype
+    assert tuple(k_pool.shape[1:]) == (kv_heads, page_size, head_dim) and tuple(v_pool.shape[1:]) == (kv_heads, page_size, value_dim)
+    _i32(block_table, "block_table")
+    tile = distance_attention_tile(head_dim, value_dim) if (SOFTMAX_ATTENTION_ON_TENSOR_CORES and q.dtype == torch.bfloat16) else 0
+    if not (tile and group <= 64 and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0 and _rows(out, "out") % 4 == 0
+            and out.data_ptr() % 8 == 0):
+        _check(lib.hfee_attention_simt_sink(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
+                                            block_table.shape[1], page_size, step.positions.data_ptr(), step.slot_of_token.data_ptr(),
+                                            out.data_ptr(), _rows(out, "attention out"), step.n, heads, kv_heads, head_dim,
+                                            value_dim, 0, float(scale), int(window or 0), 0, WEIGHTS_SOFTMAX, None, None, None, 0,
+                                            GATE_NONE, None, None, float(out_scale), _ptr(sink), _dt(q), _stream()), lib)
+        return
+    splits = 1
+    if step.max_new * group <= 16 and scratch is not None:
+        splits = getattr(step, "attention_splits", None) or attention_splits(
+            step.r, kv_heads, getattr(step, "planning_context", step.max_context))
+        if step.n * heads * splits * (tile + 2) > scratch.numel():
+            splits = 1
+    _check(lib.hfee_attention_mma_general(q.data_ptr(), _rows(q, "q"), k_pool.data_ptr(), v_pool.data_ptr(), block_table.data_ptr(),
+                                          block_table.shape[1], page_size, step.cu_tokens.data_ptr(), step.slots.data_ptr(),
+                                          step.context_before.data_ptr(), out.data_ptr(), _rows(out, "attention out"), step.n,
+                                          step.r, step.max_new, heads, kv_heads, head_dim, value_dim, float(scale), None, None,
+                                          _ptr(sink), float(out_scale), int(window or 0), splits,
+                                          _ptr(scratch) if splits > 1 else None, _stream()), lib)
+    if splits > 1:
+        count_launches(1)
+
+
+RECURRENCE_CHANNEL_DECAY, RECURRENCE_EXP_GATES = 0, 1
+
+
+def gated_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pre: torch.Tensor, bias: Optional[torch.Tensor],
+                     p0: float, q_scale: float, state: torch.Tensor, step, out: torch.Tensor, heads: int, dim: int, vdim: int,
+                     write_state: bool = True, norm_state: Optional[torch.Tensor] = None,
+                     max_state: Optional[torch.Tensor] = None) -> None:
+    """Linear attention with a gated float32 matrix state per (request slot, head), token after token.
+    RECURRENCE_CHANNEL_DECAY: S = diag(a) S + k v^T with a = sigmoid(pre + bias)^p0 per key channel (``pre`` [n, heads * dim]
+    float32, ``p0`` = 1 / tau), o = S^T q.  RECURRENCE_EXP_GATES: ``pre`` [n, 2 * heads] float32 holds the input and forget
+    gates' pre-activations x_i, x_f; i = p0 tanh(x_i / p0), f = logsigmoid(p0 tanh(x_f / p0)), m' = max(f + m, i),
+    S = e^(f + m - m') S + e^(i - m') k v^T, n likewise with k alone, o = S^T q / (max(|n . q|, e^(-m')) + 1e-6), with
+    ``norm_state`` [slots, heads, dim] and ``max_state`` [slots, heads].  ``q`` (times ``q_scale``), ``k``, ``v`` are
+    column slices of one buffer; ``state`` [slots, heads, dim, vdim]; ``out`` [n, heads * vdim] float32."""
+    lib = library()
+    ld = _rows(q, "q")
+    assert _rows(k, "k") == ld and _rows(v, "v") == ld and q.dtype == k.dtype == v.dtype
+    assert q.shape[1] == heads * dim and k.shape[1] == heads * dim and v.shape[1] == heads * vdim
+    assert pre.dtype == torch.float32 and pre.stride(1) == 1 and out.dtype == torch.float32 and out.shape[1] == heads * vdim
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous())
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
+    for t, shape in ((norm_state, (heads, dim)), (max_state, (heads,))):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape[1:]) == shape)
+    _check(lib.hfee_gated_recurrence(int(mode), q.data_ptr(), k.data_ptr(), v.data_ptr(), ld, _dt(q), pre.data_ptr(), pre.stride(0),
+                                     _ptr(bias), float(p0), float(q_scale), state.data_ptr(), _ptr(norm_state), _ptr(max_state),
+                                     step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"), step.r,
+                                     heads, dim, vdim, int(write_state), _dt(q), _stream()), lib)
+
+
+def head_norm_gate_scaled(x: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor, heads: int,
+                          head_dim: int, activation: str = "sigmoid", out_scale: float = 1.0) -> None:
+    """:func:`head_norm_gate` with the output times ``out_scale`` and a weight that is either [head_dim], shared by the
+    heads, or [heads * head_dim]."""
+    lib = library()
+    n = x.shape[0]
+    assert x.dtype == torch.float32 and gate.dtype == out.dtype and tuple(gate.shape) == tuple(x.shape) == tuple(out.shape) == (n, heads * head_dim)
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() in (head_dim, heads * head_dim)
+    per_head = weight.numel() == heads * head_dim and heads > 1
+    _check(lib.hfee_head_norm_gate_scaled(x.data_ptr(), _rows(x, "x"), weight.data_ptr(), int(per_head), float(eps), gate.data_ptr(),
+                                          _rows(gate, "gate"), out.data_ptr(), _rows(out, "out"), n, heads, head_dim,
+                                          HEAD_GATE_ACTIVATIONS[activation], float(out_scale), _dt(out), _stream()), lib)
+
 
 
 def sample(logits: torch.Tensor, out: torch.Tensor, temperature: Optional[torch.Tensor] = None,

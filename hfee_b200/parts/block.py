@@ -13,20 +13,31 @@ from .norm import LazyNormed
 class PreNormBlock(Block):
     """``x += mixer(norm(x)); x += feed_forward(norm(x))`` on the float32 residual
     stream (hostfog/hfee internal/llm/forward.go:82-114).  Built by the model with
-    its four parts already constructed."""
-    needs = ("mixer", "ffn", "mixer_norm", "ffn_norm")
+    its parts already constructed; ``ffn`` with ``ffn_norm`` is optional (a layer may have no
+    feed-forward).  ``forward(..., residual_add=e)`` first adds ``e`` to the stream, inside the
+    mixer norm's kernel when that norm can (``takes_residual_add``)."""
+    needs = ("mixer", "mixer_norm")
     graph_safe = True
 
     def __init__(self, spec, tensors, rt, parts):
         super().__init__(spec, tensors, rt, parts)
-        self.mixer, self.feed_forward = parts["mixer"], parts["ffn"]
-        self.mixer_norm, self.ffn_norm = parts["mixer_norm"], parts["ffn_norm"]
+        self.mixer, self.feed_forward = parts["mixer"], parts.get("ffn")
+        self.mixer_norm, self.ffn_norm = parts["mixer_norm"], parts.get("ffn_norm")
+        if (self.feed_forward is None) != (self.ffn_norm is None):
+            raise ValueError("a feed-forward and its input norm come together")
         self.width = int(spec.width)
+        import inspect
+        self.takes_residual_add = "residual_add" in inspect.signature(self.mixer_norm.forward).parameters
 
-    def forward(self, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool) -> None:
+    def forward(self, residual: torch.Tensor, step: Any, cache: Any, writes_cache: bool, residual_add=None) -> None:
         xn = self.rt.scratch("block_normed", (self.rt.max_tokens, self.width))[:step.n]
-        self.mixer.forward(self._normed(self.mixer, self.mixer_norm, residual, xn), residual, step, cache, writes_cache)
-        self.feed_forward.forward(self._normed(self.feed_forward, self.ffn_norm, residual, xn), residual, step)
+        if residual_add is not None:
+            self.mixer_norm.forward(residual, xn, residual_add=residual_add)
+            self.mixer.forward(xn, residual, step, cache, writes_cache)
+        else:
+            self.mixer.forward(self._normed(self.mixer, self.mixer_norm, residual, xn), residual, step, cache, writes_cache)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(self._normed(self.feed_forward, self.ffn_norm, residual, xn), residual, step)
 
     @staticmethod
     def _normed(consumer, norm, residual, buffer):

@@ -37,6 +37,38 @@ class TokenEmbedding(Part):
             ops.add_sinusoid(residual, step.positions, self.sinusoid_base)
 
 
+class BigramTokenEmbedding(Part):
+    """``x[i,:] = table[token_i,:] + pairs[r_i,:]`` with ``r_i = (previous token * mul_prev + token_i * mul_cur) mod buckets``
+    and, for a request's first token, ``r_i = buckets`` (the last row of ``pairs`` [buckets + 1, width]).
+    spec: ``vocab``, ``width``, ``buckets``, ``mul_prev``, ``mul_cur``.  The previous token of a portion's first token
+    belongs to the request: one int32 per request slot, which the model asks of the cache manager
+    (:meth:`cache_need`) and hands to ``forward`` as ``cache.state``."""
+    category = "embedding"
+    graph_safe = True
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
+        return {"table": TensorNeed((spec.vocab, spec.width), role="table"),
+                "pairs": TensorNeed((spec.buckets + 1, spec.width), role="table")}
+
+    def __init__(self, spec, tensors, rt):
+        super().__init__(spec, tensors, rt)
+        self.table, self.pairs = tensors["table"], tensors["pairs"]
+        self.buckets, self.mul_prev, self.mul_cur = int(spec.buckets), int(spec.mul_prev), int(spec.mul_cur)
+        if self.buckets < 1 or self.mul_prev < 0 or self.mul_cur < 0:
+            raise ValueError(f"bigram embedding: buckets {self.buckets} must be positive and the multipliers non-negative")
+
+    def cache_need(self):
+        from ..cache.needs import FixedState
+        return FixedState((1,), "int32")
+
+    def forward(self, step: Any, residual: torch.Tensor, cache: Any = None) -> None:
+        if cache is None or cache.state is None:
+            raise ValueError("the bigram embedding needs its per-request state (the request's last token)")
+        ops.tag("embed")
+        ops.embed_bigram(self.table, self.pairs, step, cache.state, residual, self.buckets, self.mul_prev, self.mul_cur)
+
+
 class LinearHead(Part):
     """``logits = x . W^T * scale`` in float32 (internal/llm/forward.go:132-141).  spec: ``vocab``,
     ``width``, ``tied`` (use the embedding table as W, internal/llm/model.go:118-121), ``scale``
@@ -80,4 +112,5 @@ class LinearHead(Part):
 
 
 register_part("embedding", "token", TokenEmbedding)
+register_part("embedding", "token_bigram", BigramTokenEmbedding)
 register_part("head", "linear", LinearHead)

@@ -87,6 +87,47 @@ class DenseFeedForward(Part):
         ops.linear(h, self.w_down, residual, accumulate=accumulate)
 
 
+class ClampedGluFeedForward(Part):
+    """``down(g * sigmoid(alpha * g) * (u + shift))`` with ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)``.
+    spec: ``width``, ``inner``, ``limit``, ``alpha``, ``shift`` (default 1).  ``forward(..., accumulate=False)`` stores the
+    output instead of adding it.  In bfloat16 the activation runs in the epilogue of the gate/up product for prompt
+    portions (gate and up rows stored in runs of four)."""
+    can_overwrite = True
+    category = "feed_forward"
+    graph_safe = True
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
+        return {"gate": TensorNeed((spec.inner, spec.width)), "up": TensorNeed((spec.inner, spec.width)),
+                "down": TensorNeed((spec.width, spec.inner))}
+
+    def __init__(self, spec, tensors, rt):
+        super().__init__(spec, tensors, rt)
+        self.inner, self.limit, self.alpha = int(spec.inner), float(spec.limit), float(spec.alpha)
+        self.shift = float(spec.get("shift", 1.0))
+        if self.limit <= 0:
+            raise ValueError(f"the limit must be positive, got {self.limit}")
+        gate, up = tensors["gate"], tensors["up"]
+        g = ops.SWIGLU_GRANULE
+        if gate.dtype == torch.bfloat16 and self.inner % g == 0:
+            self.granule, self.w_gate_up = g, ops.interleave_gate_up(gate, up, g)
+        else:
+            self.granule, self.w_gate_up = self.inner, torch.cat([gate, up], dim=0).contiguous()
+        self.w_down = tensors["down"]
+
+    def forward(self, xn, residual: torch.Tensor, step: Any, accumulate: bool = True) -> None:
+        from .gated_attention import pad8
+        n, rt = step.n, self.rt
+        xn = xn if isinstance(xn, torch.Tensor) else xn.tensor()
+        gu = rt.scratch("ffn_gate_up", (rt.max_tokens, pad8(2 * self.inner)))[:n, :2 * self.inner]
+        h = rt.scratch("ffn_hidden", (rt.max_tokens, pad8(self.inner)))[:n, :self.inner]
+        ops.tag("gate_up")
+        ops.linear_clamped_glu(xn, self.w_gate_up, h, self.granule, gu, self.limit, self.alpha, self.shift)
+        ops.tag("down")
+        ops.linear(h, self.w_down, residual, accumulate=accumulate)
+
+
+register_part("feed_forward", "clamped_glu", ClampedGluFeedForward)
 register_part("feed_forward", "dense", DenseFeedForward)
 register_part("feed_forward", "swiglu", SwiGLUFeedForward)
 register_part("feed_forward", "gated", SwiGLUFeedForward)       # the same part named for its general form

@@ -57,6 +57,9 @@ def model_tensor_needs(spec: ModelSpec) -> Dict[str, TensorNeed]:
     return out
 
 
+EMBEDDING_CACHE = -1        # cache id of the embedding's per-request state, beside the runs' ids (which count from 0)
+
+
 class DecoderModel:
     def __init__(self, spec: ModelSpec, checkpoint: Checkpoint, rt: Runtime):
         check_schedule(spec.layers, spec.schedule)
@@ -79,6 +82,7 @@ class DecoderModel:
             parts = {prefix: build_part(cat, ps, fetch(m, prefix), rt) for prefix, (cat, ps) in layer.parts.items()}
             self.blocks.append(part_class("block", layer.block.kind)(layer.block, {}, rt, parts=parts))
         self.width, self.vocab = spec.width, spec.vocab
+        self.keeps_embedding = any(run.adds_embedding for run in spec.schedule)
         # decode steps may be captured in CUDA graphs only if every part of the schedule allows it
         self.graph_safe = (self.embedding.graph_safe and self.final_norm.graph_safe and self.head.graph_safe
                            and all(self.blocks[run.layer].all_graph_safe for run in spec.schedule))
@@ -86,6 +90,9 @@ class DecoderModel:
     def cache_needs(self) -> Dict[int, Any]:
         """cache id -> what the writing run's mixer needs (PagedKV, FixedState or None)."""
         out: Dict[int, Any] = {}
+        need = getattr(self.embedding, "cache_need", lambda: None)()
+        if need is not None:
+            out[EMBEDDING_CACHE] = need
         for run in self.spec.schedule:
             need = self.blocks[run.layer].cache_need()
             if run.writes_cache:
@@ -107,9 +114,24 @@ class DecoderModel:
     def _forward(self, step: Any, caches: Mapping[int, Any]) -> Optional[torch.Tensor]:
         rt = self.rt
         residual = rt.scratch("residual", (rt.max_tokens, self.width), torch.float32)[:step.n]
-        self.embedding.forward(step, residual)
+        if EMBEDDING_CACHE in caches:
+            self.embedding.forward(step, residual, caches[EMBEDDING_CACHE])
+        else:
+            self.embedding.forward(step, residual)
+        embedded = None
+        if self.keeps_embedding:
+            embedded = rt.scratch("embedding_out", (rt.max_tokens, self.width), torch.float32)[:step.n]
+            embedded.copy_(residual)
         for run in self.spec.schedule:
-            self.blocks[run.layer].forward(residual, step, caches.get(run.cache), run.writes_cache)
+            block = self.blocks[run.layer]
+            if run.adds_embedding:
+                if getattr(block, "takes_residual_add", False):      # the block's first norm does the sum as well
+                    block.forward(residual, step, caches.get(run.cache), run.writes_cache, residual_add=embedded)
+                    continue
+                from ..kernels import ops
+                ops.tag("norm")
+                ops.scaled_add(embedded, 1.0, residual)
+            block.forward(residual, step, caches.get(run.cache), run.writes_cache)
         m = step.n_logits
         if m == 0:
             return None

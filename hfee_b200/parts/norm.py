@@ -1,6 +1,7 @@
-"""RMS norm part.  Formula of hostfog/hfee internal/ggml/ops.go:125-134:
+"""Norm parts.  RMS norm, formula of hostfog/hfee internal/ggml/ops.go:125-134:
 ``dst = x * 1/sqrt(mean(x^2) + eps) * weight`` per row, with the sum in float32
-here (float64 in the reference)."""
+here (float64 in the reference); and layer norm with a weight and no bias:
+``dst = (x - mean) / sqrt(mean((x - mean)^2) + eps) * weight``."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -54,6 +55,29 @@ class RMSNorm(Part):
         return self.weight, self.eps, self.add_unit
 
 
+class LayerNorm(Part):
+    """spec: ``width``, ``eps``.  Mean and variance (the mean of the squared deviations) per row in float32; a weight
+    per column, no bias."""
+    category = "norm"
+    graph_safe = True
+
+    @staticmethod
+    def tensor_needs(spec: PartSpec) -> Dict[str, TensorNeed]:
+        return {"weight": TensorNeed((spec.width,), role="scale")}
+
+    def __init__(self, spec, tensors, rt):
+        super().__init__(spec, tensors, rt)
+        self.weight = tensors["weight"]
+        self.eps = float(spec.eps)
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                residual_add: Optional[torch.Tensor] = None) -> None:
+        """``residual_add`` (float32, like ``x``): the row normed is ``x + residual_add``, and ``x`` keeps that sum."""
+        before = ops.tag("norm")
+        ops.layernorm(x, self.weight, out, self.eps, rows=rows, residual_add=residual_add)
+        ops.tag(before)
+
+
 class LazyNormed:
     """The normed input of a mixer, feed-forward or head that has not been computed yet.
 
@@ -80,3 +104,4 @@ class LazyNormed:
 
 
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "layer_norm", LayerNorm)

@@ -53,6 +53,11 @@ class ParallelMixer(Mixer):
         self.in_cols, self.inner_cols = self.w_in.shape[0], self.w_o.shape[1]
         for _, p in self.branches:          # the branches' own copies are not used again
             p.in_weight = p.w_o = None
+        self.out_bias = None
+        for (_, p), scale in zip(self.branches, self.scales):
+            if p.out_bias is not None:
+                b = p.out_bias * scale
+                self.out_bias = b if self.out_bias is None else self.out_bias + b
 
     def cache_need(self) -> CacheBundle:
         paged, states = None, {}
@@ -87,10 +92,14 @@ class ParallelMixer(Mixer):
         at_in = at_out = 0
         for (b, part), scale in zip(self.branches, self.scales):
             rows, cols = part_rows(part), part.inner_cols
-            part.mix(proj[:, at_in:at_in + rows], step, self._view(cache, b), writes_cache, inner[:, at_out:at_out + cols], scale)
+            extra = {"h": h} if part.needs_input else {}
+            part.mix(proj[:, at_in:at_in + rows], step, self._view(cache, b), writes_cache, inner[:, at_out:at_out + cols], scale,
+                     **extra)
             at_in, at_out = at_in + rows, at_out + cols
         ops.tag("o")
         ops.linear(inner, self.w_o, out, accumulate=accumulate)
+        if self.out_bias is not None:
+            ops.add_bias(out, self.out_bias)
 
 
 def part_rows(part: SplitMixer) -> int:

@@ -18,7 +18,9 @@ cut anywhere.  Gates, step sizes, decays and states are float32; the projections
 
 Both are *split mixers*: ``in_weight`` (the rows of their input projection), ``inner_cols`` and ``w_o`` are public and
 ``mix(proj, step, cache, writes_cache, into, out_scale)`` leaves what W_o reads, times ``out_scale``, in ``into``, so
-that a mixer that runs several of them side by side can project once in and once out.
+that a mixer that runs several of them side by side can project once in and once out.  A split mixer may also carry
+``out_bias`` (added after W_o) and set ``needs_input`` (its ``mix`` then gets the mixer's input as ``h=`` for a small
+product of its own).
 """
 from __future__ import annotations
 
@@ -42,6 +44,8 @@ class SplitMixer(Mixer):
     w_o: torch.Tensor
     inner_cols: int
     in_rows: int
+    out_bias = None          # float32 [width] added to the mixer's output, or None
+    needs_input = False      # True: ``mix`` also takes the mixer's input itself, as ``h=``
 
     def mix(self, proj: torch.Tensor, step: Any, cache: Any, writes_cache: bool, into: torch.Tensor, out_scale: float = 1.0) -> None:
         raise NotImplementedError
@@ -54,9 +58,14 @@ class SplitMixer(Mixer):
         ops.tag("qkv")
         ops.linear(h, self.in_weight, proj)
         inner = rt.scratch("split_inner", (rt.max_tokens, pad8(self.inner_cols)))[:n, :self.inner_cols]
-        self.mix(proj, step, cache, writes_cache, inner)
+        if self.needs_input:
+            self.mix(proj, step, cache, writes_cache, inner, h=h)
+        else:
+            self.mix(proj, step, cache, writes_cache, inner)
         ops.tag("o")
         ops.linear(inner, self.w_o, out, accumulate=accumulate)
+        if self.out_bias is not None:
+            ops.add_bias(out, self.out_bias)
 
 
 class MinGRU(SplitMixer):
