@@ -33,7 +33,7 @@ class WindowAttention:
     dim: int
     vdim: int
     scale: float
-    window: int
+    window: Optional[int]
     rot: Rotation
 
 
@@ -135,7 +135,7 @@ class PupinexConfig:
             out.append(PupinexLayer(kind, mixer, _mlp(entry.get("mlp") if isinstance(entry, Mapping) else None, where + ".mlp")))
         loop = d.get("loop")
         if loop is not None:
-            loop = Loop(_int(loop, "start", "loop"), _int(loop, "stop", "loop"), _int(loop, "times", "loop"))
+            loop = Loop(_count(loop, "start", "loop"), _count(loop, "stop", "loop"), _int(loop, "times", "loop"))
             if not (0 <= loop.start <= loop.stop <= len(out)) or loop.times < 1:
                 raise ConfigError(f"config.json: loop {loop.start}..{loop.stop} x {loop.times} does not fit {len(out)} layers")
         bigram = _get(_get(d, "embedding", "config"), "bigram", "embedding")
@@ -147,6 +147,14 @@ class PupinexConfig:
                    eps=_num(_get(d, "norm", "config"), "eps", "norm"), buckets=buckets,
                    mul_prev=_int(bigram, "mul_prev", "embedding.bigram"), mul_cur=_int(bigram, "mul_cur", "embedding.bigram"),
                    max_positions=int(max_positions))
+
+
+def _count(d: Mapping[str, Any], key: str, where: str) -> int:
+    """An integer that may be zero."""
+    v = _get(d, key, where)
+    if not isinstance(v, int) or isinstance(v, bool) or v < 0:
+        raise ConfigError(f"config.json: {where}.{key} must be a non-negative integer, got {v!r}")
+    return v
 
 
 def _positive(d: Mapping[str, Any], key: str, where: str) -> float:
@@ -161,17 +169,19 @@ def _attention(m: Mapping[str, Any], where: str) -> WindowAttention:
     if kv < 1 or heads % kv:
         raise ConfigError(f"config.json: {where}.heads {heads} must be a multiple of kv_heads {kv}")
     dim = _int(m, "dim", where)
-    rot = _get(m, "rot", where)
-    dims = _int(rot, "dims", where + ".rot")
-    if dims % 2 or not 0 <= dims <= dim:
-        raise ConfigError(f"config.json: {where}.rot.dims {dims} must be even and at most dim {dim}")
-    scaling = rot.get("scaling")
-    factor = 1.0 if scaling is None else _positive(scaling, "factor", where + ".rot.scaling")
-    window = _int(_get(m, "mask", where), "size", where + ".mask")
-    if window < 1:
-        raise ConfigError(f"config.json: {where}.mask.size must be at least 1, got {window}")
-    return WindowAttention(heads, kv, dim, _int(m, "vdim", where), _num(m, "scale", where), window,
-                           Rotation(dims, _positive(rot, "base", where + ".rot"), factor))
+    rot = m.get("rot")
+    if rot is None:                      # no rotation at all
+        rotation = Rotation(0, 1.0, 1.0)
+    else:
+        dims = _count(rot, "dims", where + ".rot")
+        if dims % 2 or dims > dim:
+            raise ConfigError(f"config.json: {where}.rot.dims {dims} must be even and at most dim {dim}")
+        scaling = rot.get("scaling")
+        factor = 1.0 if scaling is None else _positive(scaling, "factor", where + ".rot.scaling")
+        rotation = Rotation(dims, _positive(rot, "base", where + ".rot") if dims else 1.0, factor)
+    mask = m.get("mask")
+    window = None if mask is None else _int(mask, "size", where + ".mask")       # no mask: every earlier position
+    return WindowAttention(heads, kv, dim, _int(m, "vdim", where), _num(m, "scale", where), window, rotation)
 
 
 def _mlp(mlp: Optional[Mapping[str, Any]], where: str):

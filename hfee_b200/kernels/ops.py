@@ -1814,7 +1814,7 @@ def gated_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     _check(lib.hfee_gated_recurrence(int(mode), q.data_ptr(), k.data_ptr(), v.data_ptr(), ld, _dt(q), pre.data_ptr(), pre.stride(0),
                                      _ptr(bias), float(p0), float(q_scale), state.data_ptr(), _ptr(norm_state), _ptr(max_state),
                                      step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"), step.r,
-                                     heads, dim, vdim, int(write_state), _dt(q), _stream()), lib)
+                                     heads, dim, vdim, int(write_state), _stream()), lib)
 
 
 def head_norm_gate_scaled(x: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out: torch.Tensor, heads: int,

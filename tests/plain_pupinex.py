@@ -27,6 +27,7 @@ import struct
 import numpy as np
 
 SWISH_ALPHA = 1.702
+ROUTE_MARGINS = []           # per routed token: lowest chosen score minus the highest score left out (tests read it)
 
 
 def read_safetensors(path):
@@ -258,7 +259,10 @@ def routed_ffn(h, T_, p, f):
     s = sigmoid(z)
     out = np.zeros((T, T_[p + "e0.down"].shape[0]))
     for t in range(T):
-        chosen = group_limited_choice(s[t], r["top"], r["groups"]["count"], r["groups"]["keep"])
+        groups = r.get("groups") or {"count": 1, "keep": 1}
+        chosen = group_limited_choice(s[t], r["top"], groups["count"], groups["keep"])
+        left_out = [s[t, e] for e in range(len(s[t])) if e not in chosen]
+        ROUTE_MARGINS.append(min(s[t, chosen]) - max(left_out) if left_out else 1.0)
         w = s[t, chosen] / (s[t, chosen].sum() + 1e-20) * r["scale"]
         for e, we in zip(chosen, w):
             out[t] += we * silu_expert(h[t:t + 1], T_, f"{p}e{e}.")[0]
@@ -310,3 +314,11 @@ def forward(cfg, T_, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     return layer_norm(x, T_["final.norm"], eps) @ T_["embed"].T
+
+
+def greedy(cfg, T_, prompt, n):
+    """``n`` tokens after ``prompt``, each the argmax (lowest id on ties) of the logits at the last position."""
+    seq = list(prompt)
+    for _ in range(n):
+        seq.append(int(np.argmax(forward(cfg, T_, seq)[-1])))
+    return seq[len(prompt):]
