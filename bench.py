@@ -22,7 +22,10 @@ Llama model of the same width, heads, feed-forward and number of layers, with wh
 ``--design bamipel`` the same for a Bamipel model (gated delta rule, latent attention under a sliding window, gated
 grouped-query attention, norms on both sides of every sublayer, a relu^2 feed-forward); ``--design muvetar`` for a
 Muvetar model (minGRU layers in turn with softmax attention under a logarithmic distance penalty beside a selective
-scan; routed experts with a shared one whose active sizes add up to the dense feed-forward; depth averaging).
+scan; routed experts with a shared one whose active sizes add up to the dense feed-forward; depth averaging);
+``--design pupinex`` for a Pupinex model (windowed attention with normed queries and keys beside a matrix memory, windowed
+attention with a sink, gated linear attention with a decay per key channel; a clamped gated feed-forward in turn with
+group-limited routed experts and a gated shared one; a hashed bigram embedding and layer norms).
 ``--breakdown`` prints, instead of the line above, what each class of kernels costs inside the decode
 step at batch 1, 8 and 64 and inside the prompt pass: the step is timed again with that class's
 launches left out (results wrong, timing not), and the difference is the class's cost in place.
@@ -222,7 +225,34 @@ def muvetar_like(model, layers, experts=16, top=2):
             "residual_mult": 1.0, "logit_softcap": 30.0}
 
 
-DESIGNS = {"dobelix": dobelix_like, "bamipel": bamipel_like, "muvetar": muvetar_like}
+def pupinex_like(model, layers, experts=16, top=2):
+    """A Pupinex configuration of the layer sizes of the Llama configuration ``model``, layer types in turn: a parallel
+    mixer (windowed attention with the Llama heads, normed queries and keys, beside a matrix memory with as many heads as
+    the model has key/value heads, keys of the head size and values that fill the width), windowed attention with a sink,
+    gated linear attention (the same heads, keys of twice the head size, values that fill the width, a decay projection of
+    rank 16), and attention again; windows of 1,024 positions, half of every head rotated.  The attention layers carry
+    ``experts`` routed experts of a quarter of the dense feed-forward each (``top`` chosen, two groups of which one is
+    kept) and a gated shared one of half of it, the other layers the dense clamped feed-forward, so that a token passes
+    as many feed-forward weights as in the dense model.  No stretch of layers is looped."""
+    h, kv, hd = model["num_attention_heads"], model["num_key_value_heads"], model["head_dim"]
+    width, ff = model["hidden_size"], model["intermediate_size"]
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 2, "keep": 1}},
+           "expert": {"ff": ff // 4}, "shared": {"ff": ff // 2}}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    attn = lambda **more: dict({"heads": h, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": 1024}}, **more)
+    kinds = [
+        {"type": "parallel", "mlp": dense,
+         "mixer": {"left": attn(rot={"dims": hd // 2, "base": 500000.0, "scaling": {"factor": 4.0}}),
+                   "right": {"heads": kv, "dim": hd, "vdim": width // kv, "gate_cap": 15.0}, "left_scale": 1.0, "right_scale": 1.0}},
+        {"type": "attention", "mlp": moe, "mixer": attn(rot={"dims": hd // 2, "base": 500000.0})},
+        {"type": "gla", "mlp": dense, "mixer": {"heads": kv, "dim": 2 * hd, "vdim": width // kv, "tau": 16.0, "rank": 16}},
+        {"type": "attention", "mlp": moe, "mixer": attn(rot={"dims": hd // 2, "base": 500000.0})},
+    ]
+    return {"architecture": "Pupinex", "vocab": model["vocab_size"], "width": width, "layers": [kinds[i % 4] for i in range(layers)],
+            "norm": {"eps": 1e-5}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}}
+
+
+DESIGNS = {"dobelix": dobelix_like, "bamipel": bamipel_like, "muvetar": muvetar_like, "pupinex": pupinex_like}
 # kernel classes (the names the parts tag their launches with) that only some layers of a design have: class -> the layer
 # types that have it; every other class is counted once per layer ("head": once per model)
 DESIGN_CLASSES = {
@@ -232,6 +262,8 @@ DESIGN_CLASSES = {
                 "attention": ("attention", "latent_attention"), "fold": ("latent_attention",), "expand": ("latent_attention",)},
     "muvetar": {"conv": ("parallel",), "scan_proj": ("parallel",), "scan": ("parallel", "mingru"), "rope": ("parallel",),
                 "attention": ("parallel",), "router": ("parallel", "mingru"), "experts": ("parallel", "mingru")},
+    "pupinex": {"rope": ("parallel", "attention"), "attention": ("parallel", "attention"), "scan_proj": ("parallel", "gla"),
+                "linear_attention": ("parallel", "gla"), "gate": ("parallel", "gla"), "router": ("attention",), "experts": ("attention",)},
 }
 CLASS_ORDER = ("conv", "norm", "qkv", "rope", "fold", "attention", "expand", "linear_attention", "delta_rule", "scan_proj", "scan",
                "gate", "o", "router", "experts", "gate_up", "up", "down", "head")

@@ -102,6 +102,7 @@ _SIGNATURES = {
     "hfee_attention_mma_general": [_P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P, _P, _P, _F, _I,
                                    _I, _P, _P],
     "hfee_gated_recurrence": [_I, _P, _P, _P, _L, _I, _P, _L, _P, _F, _F, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
+    "hfee_gated_recurrence_chunked": [_I, _P, _P, _P, _L, _I, _P, _L, _P, _F, _F, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P, _L, _P],
     "hfee_head_norm_gate_scaled": [_P, _L, _P, _I, _F, _P, _L, _P, _L, _I, _I, _I, _I, _F, _I, _P],
     "hfee_moe_combine_extra": [_P, _P, _P, _I, _I, _P, _I, _I, _P, _P, _L, _P],
     "hfee_moe_route_grouped": [_P, _L, _I, _I, _I, _I, _I, _F, _P, _P, _P],
@@ -139,6 +140,8 @@ def library() -> ctypes.CDLL:
     lib.hfee_linear_attention_chunked_workspace.argtypes = [_I, _I, _I, _I, _I]
     lib.hfee_delta_rule_workspace.restype = _L
     lib.hfee_delta_rule_workspace.argtypes = [_I, _I, _I, _I, _I]
+    lib.hfee_gated_recurrence_workspace.restype = _L
+    lib.hfee_gated_recurrence_workspace.argtypes = [_I, _I, _I, _I, _I]
     lib.hfee_moe_tile_rows.restype = _I
     lib.hfee_moe_tile_rows.argtypes = []
     for name, sig in _SIGNATURES.items():
@@ -1789,19 +1792,27 @@ def softmax_attention(q, k_pool, v_pool, block_table, page_size, step, out, head
 
 
 RECURRENCE_CHANNEL_DECAY, RECURRENCE_EXP_GATES = 0, 1
+RECURRENCE_CHUNKED_MIN = 65        # from this many new tokens of one request on, runs of 64 tokens work side by side
+
+
+def gated_recurrence_workspace(requests: int, tokens: int, heads: int, dim: int, vdim: int) -> int:
+    """Floats of workspace :func:`gated_recurrence` wants for steps of at most ``tokens`` tokens of ``requests`` requests."""
+    return int(library().hfee_gated_recurrence_workspace(requests, tokens, heads, dim, vdim))
 
 
 def gated_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pre: torch.Tensor, bias: Optional[torch.Tensor],
                      p0: float, q_scale: float, state: torch.Tensor, step, out: torch.Tensor, heads: int, dim: int, vdim: int,
                      write_state: bool = True, norm_state: Optional[torch.Tensor] = None,
-                     max_state: Optional[torch.Tensor] = None) -> None:
+                     max_state: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> None:
     """Linear attention with a gated float32 matrix state per (request slot, head), token after token.
     RECURRENCE_CHANNEL_DECAY: S = diag(a) S + k v^T with a = sigmoid(pre + bias)^p0 per key channel (``pre`` [n, heads * dim]
     float32, ``p0`` = 1 / tau), o = S^T q.  RECURRENCE_EXP_GATES: ``pre`` [n, 2 * heads] float32 holds the input and forget
     gates' pre-activations x_i, x_f; i = p0 tanh(x_i / p0), f = logsigmoid(p0 tanh(x_f / p0)), m' = max(f + m, i),
     S = e^(f + m - m') S + e^(i - m') k v^T, n likewise with k alone, o = S^T q / (max(|n . q|, e^(-m')) + 1e-6), with
     ``norm_state`` [slots, heads, dim] and ``max_state`` [slots, heads].  ``q`` (times ``q_scale``), ``k``, ``v`` are
-    column slices of one buffer; ``state`` [slots, heads, dim, vdim]; ``out`` [n, heads * vdim] float32."""
+    column slices of one buffer; ``state`` [slots, heads, dim, vdim]; ``out`` [n, heads * vdim] float32.  With ``workspace``
+    (float32, :func:`gated_recurrence_workspace`) and a request that brings RECURRENCE_CHUNKED_MIN tokens or more, runs of 64
+    tokens are walked side by side (the same recurrence in another association)."""
     lib = library()
     ld = _rows(q, "q")
     assert _rows(k, "k") == ld and _rows(v, "v") == ld and q.dtype == k.dtype == v.dtype
@@ -1811,6 +1822,15 @@ def gated_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
     for t, shape in ((norm_state, (heads, dim)), (max_state, (heads,))):
         assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape[1:]) == shape)
+    if workspace is not None and step.max_new >= RECURRENCE_CHUNKED_MIN:
+        assert workspace.dtype == torch.float32 and workspace.is_contiguous()
+        _check(lib.hfee_gated_recurrence_chunked(int(mode), q.data_ptr(), k.data_ptr(), v.data_ptr(), ld, _dt(q), pre.data_ptr(),
+                                                 pre.stride(0), _ptr(bias), float(p0), float(q_scale), state.data_ptr(),
+                                                 _ptr(norm_state), _ptr(max_state), step.cu_tokens.data_ptr(), step.slots.data_ptr(),
+                                                 out.data_ptr(), _rows(out, "out"), step.r, step.n, heads, dim, vdim,
+                                                 int(write_state), workspace.data_ptr(), workspace.numel(), _stream()), lib)
+        count_launches(2 + int(mode == RECURRENCE_EXP_GATES))
+        return
     _check(lib.hfee_gated_recurrence(int(mode), q.data_ptr(), k.data_ptr(), v.data_ptr(), ld, _dt(q), pre.data_ptr(), pre.stride(0),
                                      _ptr(bias), float(p0), float(q_scale), state.data_ptr(), _ptr(norm_state), _ptr(max_state),
                                      step.cu_tokens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), _rows(out, "out"), step.r,

@@ -34,6 +34,15 @@ from .gated_attention import pad8
 from .recurrent import SplitMixer
 
 
+def _workspace(part, step):
+    """The chunked path's workspace, sized once for the engine's limits, for steps that take that path."""
+    if step.max_new < ops.RECURRENCE_CHUNKED_MIN:
+        return None
+    rt = part.rt
+    return rt.scratch("recurrence_runs", (ops.gated_recurrence_workspace(rt.max_requests, rt.max_tokens, part.heads, part.key_dim,
+                                                                         part.value_dim),), torch.float32)
+
+
 class ChannelDecayAttention(SplitMixer):
     """spec: ``width``, ``heads``, ``key_dim``, ``value_dim``, ``decay_rank`` (rows of W_a1), ``tau``, ``eps`` (of the
     output norm).  Tensors: ``q``, ``k`` [heads * key_dim, width], ``v``, ``g`` [heads * value_dim, width], ``a1``
@@ -76,7 +85,7 @@ class ChannelDecayAttention(SplitMixer):
         ops.tag("linear_attention")
         ops.gated_recurrence(ops.RECURRENCE_CHANNEL_DECAY, proj[:, :a], proj[:, a:b], proj[:, b:c], z, self.a2_bias,
                              1.0 / self.tau, self.key_dim ** -0.5, state, step, o, self.heads, self.key_dim, self.value_dim,
-                             writes_cache)
+                             writes_cache, workspace=_workspace(self, step))
         ops.tag("gate")
         ops.head_norm_gate_scaled(o, self.norm_weight, self.eps, proj[:, c:d], into, self.heads, self.value_dim, "silu", out_scale)
 
@@ -128,7 +137,7 @@ class MatrixMemory(SplitMixer):
         ops.tag("linear_attention")
         ops.gated_recurrence(ops.RECURRENCE_EXP_GATES, proj[:, :a], proj[:, a:b], proj[:, b:c], gates, self.gate_bias, self.cap,
                              self.key_dim ** -0.5, cache.states["memory"], step, o, self.heads, self.key_dim, self.value_dim,
-                             writes_cache, cache.states["normalizer"], cache.states["maximum"])
+                             writes_cache, cache.states["normalizer"], cache.states["maximum"], _workspace(self, step))
         ops.tag("gate")
         ops.head_norm_gate_scaled(o, self.norm_weight, self.eps, proj[:, c:d], into, self.heads, self.value_dim, "sigmoid", out_scale)
 

@@ -243,6 +243,45 @@ def test_gated_recurrence_continues_across_portions(dtype, mode, heads, dim, vdi
     assert torch.equal(S, before)                                  # a run that must not write the state does not
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 16, 24), (1, 70, 40), (2, 128, 64)])
+def test_gated_recurrence_in_runs_of_tokens(mode, heads, dim, vdim):
+    """Long portions are walked as runs of 64 tokens side by side: portions that end inside a run, at its edge and one
+    behind it, next to a single token and a short portion, continue the same states as the walk token by token."""
+    from hfee_b200.kernels import ops
+    rng = np.random.default_rng(heads * dim + mode + 7)
+    lens, slots = [64 + 130 + 65, 1 + 1 + 3, 9 + 128 + 1], [1, 3, 0]
+    qk, vc = heads * dim, heads * vdim
+    proj = [dev(rng.normal(size=(n, 2 * qk + vc)) * 0.7) for n in lens]
+    pre_cols = qk if mode == 0 else 2 * heads
+    pre = [rng.normal(size=(n, pre_cols)) * 2.0 for n in lens]
+    bias = rng.normal(size=pre_cols) + (2.0 if mode == 0 else 0.0)
+    p0, q_scale = (0.5, dim ** -0.5) if mode == 0 else (6.0, dim ** -0.5)
+    S, N, M = torch.zeros((4, heads, dim, vdim), device=DEV), torch.zeros((4, heads, dim), device=DEV), torch.zeros((4, heads), device=DEV)
+    want = []
+    for x, z in zip(proj, pre):
+        xf, n = x.cpu().numpy().astype(np.float64), x.shape[0]
+        o, _ = plain_recurrence(mode, xf[:, :qk].reshape(n, heads, dim) * q_scale, xf[:, qk:2 * qk].reshape(n, heads, dim),
+                                xf[:, 2 * qk:].reshape(n, heads, vdim), z, bias, p0,
+                                (np.zeros((heads, dim, vdim)), np.zeros((heads, dim)), np.zeros(heads)))
+        want.append(o.reshape(n, vc))
+    ws = torch.empty((ops.gated_recurrence_workspace(4, 512, heads, dim, vdim),), device=DEV)
+    got, at = [[] for _ in lens], [0, 0, 0]
+    for sizes in ([64, 1, 9], [130, 1, 128], [65, 3, 1]):
+        x = torch.cat([proj[i][at[i]:at[i] + sizes[i]] for i in range(3)])
+        z = dev(np.concatenate([pre[i][at[i]:at[i] + sizes[i]] for i in range(3)]))
+        step = make_step(sizes, slots=slots)
+        out = torch.empty((x.shape[0], vc), device=DEV)
+        ops.gated_recurrence(mode, x[:, :qk], x[:, qk:2 * qk], x[:, 2 * qk:], z, dev(bias), p0, q_scale, S, step, out, heads, dim, vdim,
+                             True, N if mode else None, M if mode else None, ws if max(sizes) >= ops.RECURRENCE_CHUNKED_MIN else None)
+        o, j = out.cpu().numpy(), 0
+        for i in range(3):
+            got[i].append(o[j:j + sizes[i]]); j += sizes[i]; at[i] += sizes[i]
+    for g, w in zip(got, want):
+        assert close(np.concatenate(g), w, 3e-5)
+    assert float(S[2].abs().sum()) == 0.0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,head_dim,per_head,act", [(3, 24, False, "silu"), (2, 40, True, "sigmoid"), (1, 7, True, "silu"), (5, 64, False, "sigmoid")])
 def test_head_norm_gate_with_weights_per_head_and_a_scale(dtype, heads, head_dim, per_head, act):
