@@ -11,9 +11,10 @@
 // projection buffer (type T); the gates' pre-activations z, x_i, x_f are float32, and so are the decays, their
 // logarithms and exponentials, the states, every product and o.
 //
-// hfee_gated_recurrence walks a request's tokens one after the other.  A thread keeps GR_ROWS rows of one state
-// column in registers; a warp covers GR_COLS = 32 columns of those rows, a block all rows (blockDim.y row groups whose
-// partial outputs meet in shared memory in a fixed order) of 32 columns; blockIdx = (head, request, column tile).
+// hfee_gated_recurrence walks a request's tokens one after the other.  A thread keeps GR_ROWS rows
+// of two state columns in registers (a staged q, k or decay is read from shared memory once for both); a warp covers
+// GR_COLS = 64 columns of those rows, a block all rows (blockDim.y row groups whose partial outputs meet in shared
+// memory in a fixed order) of 64 columns; blockIdx = (head, request, column tile).
 // Lane j of row group g also keeps n[g * 32 + j].  Tokens are staged GR_STAGE at a time; the scalar recurrence of
 // the running maximum is walked by one thread per stage.  The order of the sums does not depend on how a prompt was
 // cut, and a state is what the tokens before left, so neither does a position's output.
@@ -29,7 +30,9 @@
 namespace {
 
 constexpr int GR_ROWS = 32;
-constexpr int GR_COLS = 32;
+constexpr int GR_LANES = 32;         // threads of a row group: one warp
+constexpr int GR_NC = 2;             // state columns per thread (lane j: columns j and j + 32 of the block's 64)
+constexpr int GR_COLS = GR_LANES * GR_NC;
 constexpr int GR_STAGE = 8;
 constexpr int GR_MAX_DIM = 256;
 constexpr int GC_T = 64;             // tokens of a run of the chunked path
@@ -61,6 +64,7 @@ struct RecurrenceArgs {
   float* run_decay;             // [runs, heads, dim]        product of the run's decays per key channel
   const float* gates;           // [3][n_tokens, heads]: a_t, b_t, e^(-m_t) (exponential gates)
   long long gate_stride;        // n_tokens * heads
+  int decays_given;             // channel decay: `pre` holds the decays themselves (the chunked path computes them once)
 };
 
 __device__ __forceinline__ int runs_of(int count) { return (count + GC_T - 1) / GC_T; }
@@ -77,7 +81,7 @@ __device__ __forceinline__ bool find_run(const int* __restrict__ cu_tokens, int 
 }
 
 template <typename T, int MODE, int PASS>
-__global__ void __launch_bounds__(GR_COLS * (GR_MAX_DIM / GR_ROWS))
+__global__ void __launch_bounds__(GR_LANES * (GR_MAX_DIM / GR_ROWS), 2)
 gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, RecurrenceArgs p) {
   extern __shared__ __align__(16) float smem[];
   __shared__ float a_s[GR_STAGE], b_s[GR_STAGE], em_s[GR_STAGE];
@@ -89,8 +93,8 @@ gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
   }
   const int groups = blockDim.y, dim_pad = groups * GR_ROWS;
   const int j = threadIdx.x, g = threadIdx.y;
-  const int col = blockIdx.z * GR_COLS + j;
-  const int tid = g * GR_COLS + j, threads = GR_COLS * groups;
+  const int col = blockIdx.z * GR_COLS + j;            // and col + 32
+  const int tid = g * GR_LANES + j, threads = GR_LANES * groups;
   const int heads = p.heads, dim = p.dim, vdim = p.vdim;
   float* qs = smem;                                   // [GR_STAGE][dim_pad]
   float* ks = qs + GR_STAGE * dim_pad;                // [GR_STAGE][dim_pad]
@@ -112,12 +116,14 @@ gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
   const long long place = PASS == PASS_WHOLE ? (long long)slot * heads + head : (long long)blockIdx.y * heads + head;
   float* S_g = (PASS == PASS_WHOLE ? p.state : p.run_state) + (place * dim) * vdim;
   float* n_g = (PASS == PASS_WHOLE ? p.norm_state : p.run_norm) + place * dim;
-  float S[GR_ROWS];
+  float S[GR_NC][GR_ROWS];
 #pragma unroll
-  for (int i = 0; i < GR_ROWS; ++i) {
-    const int row = g * GR_ROWS + i;
-    S[i] = (PASS != PASS_LOCAL && row < dim && col < vdim) ? S_g[(long long)row * vdim + col] : 0.f;
-  }
+  for (int c = 0; c < GR_NC; ++c)
+#pragma unroll
+    for (int i = 0; i < GR_ROWS; ++i) {
+      const int row = g * GR_ROWS + i;
+      S[c][i] = (PASS != PASS_LOCAL && row < dim && col + c * GR_LANES < vdim) ? S_g[(long long)row * vdim + col + c * GR_LANES] : 0.f;
+    }
   float n_own = 0.f;                                  // n[g * GR_ROWS + j]
   float decay_own = 1.f;                              // PASS_LOCAL: product of the run's decays of that row
   const int own_row = g * GR_ROWS + j;
@@ -125,22 +131,29 @@ gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
     if (PASS != PASS_LOCAL && own_row < dim) n_own = n_g[own_row];
     if (PASS == PASS_WHOLE && tid == 0) m_cur = p.max_state[(long long)slot * heads + head];
   }
+  // A block has as many threads as a staged token has (padded) key channels: thread `tid` brings channel `tid` of every
+  // token of a stage, and its share of the stage's values.
+  const bool live_d = tid < dim;
+  const int chan = head * dim + tid;
+  const float z_bias = (MODE == MODE_CHANNEL_DECAY && live_d && !p.decays_given && p.bias != nullptr) ? p.bias[chan] : 0.f;
   for (int t0 = 0; t0 < count; t0 += GR_STAGE) {
     const int nt = min(GR_STAGE, count - t0);
     __syncthreads();                                  // the stage before is used up
-    for (int e = tid; e < nt * dim_pad; e += threads) {
-      const int t = e / dim_pad, d = e % dim_pad;
-      const long long at = (long long)(begin + t0 + t) * p.ld + (long long)head * dim + d;
-      qs[e] = d < dim ? to_f32<T>(q[at]) * p.q_scale : 0.f;
-      ks[e] = d < dim ? to_f32<T>(k[at]) : 0.f;
-      if constexpr (MODE == MODE_CHANNEL_DECAY) {
-        float a = 1.f;
-        if (d < dim) {
-          const int c = head * dim + d;
-          const float z = p.pre[(long long)(begin + t0 + t) * p.ld_pre + c] + (p.bias != nullptr ? p.bias[c] : 0.f);
-          a = expf(log_sigmoid_f32(z) * p.p0);
+#pragma unroll
+    for (int t = 0; t < GR_STAGE; ++t) {
+      if (t < nt) {
+        const int e = t * dim_pad + tid;
+        const long long at = (long long)(begin + t0 + t) * p.ld + chan;
+        qs[e] = live_d ? to_f32<T>(q[at]) * p.q_scale : 0.f;
+        ks[e] = live_d ? to_f32<T>(k[at]) : 0.f;
+        if constexpr (MODE == MODE_CHANNEL_DECAY) {    // a decay, or the gate's pre-activation it comes from
+          float a = 1.f;
+          if (live_d) {
+            a = p.pre[(long long)(begin + t0 + t) * p.ld_pre + chan];
+            if (!p.decays_given) a = expf(log_sigmoid_f32(a + z_bias) * p.p0);
+          }
+          as[e] = a;
         }
-        as[e] = a;
       }
     }
     for (int e = tid; e < nt * GR_COLS; e += threads) {
@@ -176,30 +189,38 @@ gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
     }
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
-      const float vv = vs[t * GR_COLS + j];
+      const float vv = vs[t * GR_COLS + j], vw = vs[t * GR_COLS + GR_LANES + j];
       const float4* k4 = reinterpret_cast<const float4*>(ks + t * dim_pad + g * GR_ROWS);
       const float4* q4 = reinterpret_cast<const float4*>(qs + t * dim_pad + g * GR_ROWS);
-      float acc = 0.f;
+      float acc = 0.f, acd = 0.f;
       if constexpr (MODE == MODE_CHANNEL_DECAY) {
         const float4* a4 = reinterpret_cast<const float4*>(as + t * dim_pad + g * GR_ROWS);
 #pragma unroll
         for (int i = 0; i < GR_ROWS / 4; ++i) {
           const float4 kk = k4[i], qq = q4[i], aa = a4[i];
-          S[4 * i + 0] = fmaf(aa.x, S[4 * i + 0], kk.x * vv);  acc = fmaf(S[4 * i + 0], qq.x, acc);
-          S[4 * i + 1] = fmaf(aa.y, S[4 * i + 1], kk.y * vv);  acc = fmaf(S[4 * i + 1], qq.y, acc);
-          S[4 * i + 2] = fmaf(aa.z, S[4 * i + 2], kk.z * vv);  acc = fmaf(S[4 * i + 2], qq.z, acc);
-          S[4 * i + 3] = fmaf(aa.w, S[4 * i + 3], kk.w * vv);  acc = fmaf(S[4 * i + 3], qq.w, acc);
+          S[0][4 * i + 0] = fmaf(aa.x, S[0][4 * i + 0], kk.x * vv);  acc = fmaf(S[0][4 * i + 0], qq.x, acc);
+          S[0][4 * i + 1] = fmaf(aa.y, S[0][4 * i + 1], kk.y * vv);  acc = fmaf(S[0][4 * i + 1], qq.y, acc);
+          S[0][4 * i + 2] = fmaf(aa.z, S[0][4 * i + 2], kk.z * vv);  acc = fmaf(S[0][4 * i + 2], qq.z, acc);
+          S[0][4 * i + 3] = fmaf(aa.w, S[0][4 * i + 3], kk.w * vv);  acc = fmaf(S[0][4 * i + 3], qq.w, acc);
+          S[1][4 * i + 0] = fmaf(aa.x, S[1][4 * i + 0], kk.x * vw);  acd = fmaf(S[1][4 * i + 0], qq.x, acd);
+          S[1][4 * i + 1] = fmaf(aa.y, S[1][4 * i + 1], kk.y * vw);  acd = fmaf(S[1][4 * i + 1], qq.y, acd);
+          S[1][4 * i + 2] = fmaf(aa.z, S[1][4 * i + 2], kk.z * vw);  acd = fmaf(S[1][4 * i + 2], qq.z, acd);
+          S[1][4 * i + 3] = fmaf(aa.w, S[1][4 * i + 3], kk.w * vw);  acd = fmaf(S[1][4 * i + 3], qq.w, acd);
         }
         if constexpr (PASS == PASS_LOCAL) decay_own *= as[t * dim_pad + own_row];
       } else {
-        const float a = a_s[t], bv = b_s[t] * vv;
+        const float a = a_s[t], bv = b_s[t] * vv, bw = b_s[t] * vw;
 #pragma unroll
         for (int i = 0; i < GR_ROWS / 4; ++i) {
           const float4 kk = k4[i], qq = q4[i];
-          S[4 * i + 0] = fmaf(a, S[4 * i + 0], kk.x * bv);  acc = fmaf(S[4 * i + 0], qq.x, acc);
-          S[4 * i + 1] = fmaf(a, S[4 * i + 1], kk.y * bv);  acc = fmaf(S[4 * i + 1], qq.y, acc);
-          S[4 * i + 2] = fmaf(a, S[4 * i + 2], kk.z * bv);  acc = fmaf(S[4 * i + 2], qq.z, acc);
-          S[4 * i + 3] = fmaf(a, S[4 * i + 3], kk.w * bv);  acc = fmaf(S[4 * i + 3], qq.w, acc);
+          S[0][4 * i + 0] = fmaf(a, S[0][4 * i + 0], kk.x * bv);  acc = fmaf(S[0][4 * i + 0], qq.x, acc);
+          S[0][4 * i + 1] = fmaf(a, S[0][4 * i + 1], kk.y * bv);  acc = fmaf(S[0][4 * i + 1], qq.y, acc);
+          S[0][4 * i + 2] = fmaf(a, S[0][4 * i + 2], kk.z * bv);  acc = fmaf(S[0][4 * i + 2], qq.z, acc);
+          S[0][4 * i + 3] = fmaf(a, S[0][4 * i + 3], kk.w * bv);  acc = fmaf(S[0][4 * i + 3], qq.w, acc);
+          S[1][4 * i + 0] = fmaf(a, S[1][4 * i + 0], kk.x * bw);  acd = fmaf(S[1][4 * i + 0], qq.x, acd);
+          S[1][4 * i + 1] = fmaf(a, S[1][4 * i + 1], kk.y * bw);  acd = fmaf(S[1][4 * i + 1], qq.y, acd);
+          S[1][4 * i + 2] = fmaf(a, S[1][4 * i + 2], kk.z * bw);  acd = fmaf(S[1][4 * i + 2], qq.z, acd);
+          S[1][4 * i + 3] = fmaf(a, S[1][4 * i + 3], kk.w * bw);  acd = fmaf(S[1][4 * i + 3], qq.w, acd);
         }
         n_own = fmaf(a, n_own, b_s[t] * ks[t * dim_pad + own_row]);
         if constexpr (PASS == PASS_LOCAL) decay_own *= a;
@@ -208,7 +229,10 @@ gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
           if (j == 0) part_n[t * groups + g] = nq;
         }
       }
-      if constexpr (PASS != PASS_LOCAL) part[(t * groups + g) * GR_COLS + j] = acc;
+      if constexpr (PASS != PASS_LOCAL) {
+        part[(t * groups + g) * GR_COLS + j] = acc;
+        part[(t * groups + g) * GR_COLS + GR_LANES + j] = acd;
+      }
     }
     if constexpr (PASS == PASS_LOCAL) continue;       // a run's own sum: no outputs
     __syncthreads();
@@ -227,10 +251,12 @@ gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
   if constexpr (PASS == PASS_OUT) return;
   if (PASS == PASS_LOCAL || p.write_state) {
 #pragma unroll
-    for (int i = 0; i < GR_ROWS; ++i) {
-      const int row = g * GR_ROWS + i;
-      if (row < dim && col < vdim) S_g[(long long)row * vdim + col] = S[i];
-    }
+    for (int c = 0; c < GR_NC; ++c)
+#pragma unroll
+      for (int i = 0; i < GR_ROWS; ++i) {
+        const int row = g * GR_ROWS + i;
+        if (row < dim && col + c * GR_LANES < vdim) S_g[(long long)row * vdim + col + c * GR_LANES] = S[c][i];
+      }
     if (blockIdx.z == 0) {
       if constexpr (MODE == MODE_EXP_GATES) {
         if (own_row < dim) n_g[own_row] = n_own;
@@ -241,6 +267,19 @@ gated_recurrence_kernel(const T* __restrict__ q, const T* __restrict__ k, const 
       }
     }
   }
+}
+
+// pre[t, c] <- sigmoid(pre[t, c] + bias[c])^p0: every token's decays, once for all passes and column tiles.
+__global__ void __launch_bounds__(256)
+channel_decays_kernel(float* __restrict__ pre, long long ld_pre, const float* __restrict__ bias, float p0, int cols, long long total) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long e = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (e >= total) return;
+  const long long r = e / cols;
+  const int c = (int)(e - r * cols);
+  float* at = pre + r * ld_pre + c;
+  *at = expf(log_sigmoid_f32(*at + (bias != nullptr ? bias[c] : 0.f)) * p0);
 }
 
 // Every token's gates of the exponential recurrence, one warp per (request, head).  The running maximum is the map
@@ -261,14 +300,29 @@ memory_gates_kernel(const float* __restrict__ pre, long long ld_pre, const float
   if (count <= 0) return;
   float m = max_state[(long long)slot * heads + head];
   const float bi = bias != nullptr ? bias[head] : 0.f, bf = bias != nullptr ? bias[heads + head] : 0.f;
+  constexpr int AHEAD = 4;                             // groups of 32 tokens whose pre-activations are requested together
+  float xi[AHEAD], xf[AHEAD];
   for (int t0 = 0; t0 < count; t0 += 32) {
     const int t = t0 + lane;
     const bool live = t < count;
+    const int u = (t0 / 32) % AHEAD;
+    if (u == 0) {
+#pragma unroll
+      for (int i = 0; i < AHEAD; ++i) {
+        const int ti = t + 32 * i;
+        const float* row = pre + (long long)(begin + min(ti, count - 1)) * ld_pre;
+        xi[i] = row[head];
+        xf[i] = row[heads + head];
+      }
+    }
     float ig = -INFINITY, fg = 0.f;                    // a dead lane is the identity map
     if (live) {
-      const float* row = pre + (long long)(begin + t) * ld_pre;
-      ig = cap * tanhf((row[head] + bi) / cap);
-      fg = log_sigmoid_f32(cap * tanhf((row[heads + head] + bf) / cap));
+      float vi = xi[0], vf = xf[0];
+#pragma unroll
+      for (int i = 1; i < AHEAD; ++i)
+        if (u == i) { vi = xi[i]; vf = xf[i]; }
+      ig = cap * tanhf((vi + bi) / cap);
+      fg = log_sigmoid_f32(cap * tanhf((vf + bf) / cap));
     }
     float F = fg, I = ig;                              // the maps of tokens t0 .. t composed
 #pragma unroll
@@ -308,12 +362,21 @@ recurrence_carry_kernel(RecurrenceArgs p, int with_norm) {
     const int row = (int)(e / p.vdim);
     float* S_g = p.state + ((long long)slot * p.heads + head) * elements + e;
     float S = *S_g;
-    for (int c = 0; c < runs; ++c) {
-      const long long place = (long long)(first + c) * p.heads + head;
-      float* w = p.run_state + place * elements + e;
-      const float own = *w;
-      *w = S;
-      S = fmaf(p.run_decay[place * p.dim + row], S, own);
+    for (int c0 = 0; c0 < runs; c0 += 8) {              // eight runs' sums and decays are requested together
+      float own[8], dec[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const long long place = (long long)(first + min(c0 + i, runs - 1)) * p.heads + head;
+        own[i] = p.run_state[place * elements + e];
+        dec[i] = p.run_decay[place * p.dim + row];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (c0 + i < runs) {
+          p.run_state[((long long)(first + c0 + i) * p.heads + head) * elements + e] = S;
+          S = fmaf(dec[i], S, own[i]);
+        }
+      }
     }
     if (p.write_state && runs > 0) *S_g = S;
   }
@@ -335,7 +398,7 @@ template <typename T, int PASS>
 int launch_recurrence(int mode, const void* q, const void* k, const void* v, const RecurrenceArgs& p, int grid_y,
                       cudaStream_t stream) {
   const int groups = (p.dim + GR_ROWS - 1) / GR_ROWS, dim_pad = groups * GR_ROWS;
-  const dim3 grid(p.heads, grid_y, (p.vdim + GR_COLS - 1) / GR_COLS), block(GR_COLS, groups);
+  const dim3 grid(p.heads, grid_y, (p.vdim + GR_COLS - 1) / GR_COLS), block(GR_LANES, groups);
   size_t floats = (size_t)GR_STAGE * (2 * dim_pad + GR_COLS + groups * GR_COLS + groups);
   if (mode == MODE_CHANNEL_DECAY) floats += (size_t)GR_STAGE * dim_pad;
   const size_t smem = floats * sizeof(float);
@@ -347,8 +410,16 @@ int launch_recurrence(int mode, const void* q, const void* k, const void* v, con
 }
 
 template <typename T>
-int launch_chunked(int mode, const void* q, const void* k, const void* v, const RecurrenceArgs& p, const float* pre, long long ld_pre,
+int launch_chunked(int mode, const void* q, const void* k, const void* v, RecurrenceArgs p, const float* pre, long long ld_pre,
                    const float* bias, float cap, int n_tokens, int max_runs, cudaStream_t stream) {
+  if (mode == MODE_CHANNEL_DECAY) {                  // `pre` is scratch of the caller's: the decays take the gates' place
+    const int cols = p.heads * p.dim;
+    const long long total = (long long)n_tokens * cols;
+    hfee_launch(channel_decays_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (float*)pre, ld_pre, bias, p.p0, cols, total);
+    int rc = hfee_check_launch("channel_decays");
+    if (rc != HFEE_OK) return rc;
+    p.decays_given = 1;
+  }
   if (mode == MODE_EXP_GATES) {
     hfee_launch(memory_gates_kernel, dim3((p.requests * p.heads + 3) / 4), dim3(128), 0, stream, pre, ld_pre, bias, cap, p.max_state,
                 p.cu_tokens, p.slots, p.requests, p.heads, (float*)p.gates, p.gate_stride, p.write_state);
@@ -385,7 +456,7 @@ HFEE_API int hfee_gated_recurrence(int mode, const void* q, const void* k, const
   HFEE_REQUIRE(mode == MODE_CHANNEL_DECAY || (norm_state != nullptr && max_state != nullptr), "gated_recurrence: exponential gates need their normaliser and maximum states");
   HFEE_REQUIRE(p0 > 0.f, "gated_recurrence: the temperature or cap must be positive");
   RecurrenceArgs p{ld, pre, ld_pre, bias, p0, q_scale, state, norm_state, max_state, cu_tokens, slots, out, ld_o, heads, dim, vdim, write_state,
-                   requests, nullptr, nullptr, nullptr, nullptr, 0};
+                   requests, nullptr, nullptr, nullptr, nullptr, 0, 0};
   if (dtype == HFEE_F32) return launch_recurrence<float, PASS_WHOLE>(mode, q, k, v, p, requests, stream);
   if (dtype == HFEE_BF16) return launch_recurrence<__nv_bfloat16, PASS_WHOLE>(mode, q, k, v, p, requests, stream);
   return hfee_fail(HFEE_ERR_ARG, "gated_recurrence: unknown dtype %d", dtype);
@@ -398,9 +469,10 @@ HFEE_API long long hfee_gated_recurrence_workspace(int requests, int n_tokens, i
 }
 
 // The same result as hfee_gated_recurrence for steps with long portions; `workspace` holds
-// hfee_gated_recurrence_workspace(requests, n_tokens, ...) floats.
+// hfee_gated_recurrence_workspace(requests, n_tokens, ...) floats.  With the channel decay, `pre` is overwritten (by the
+// decays).
 HFEE_API int hfee_gated_recurrence_chunked(int mode, const void* q, const void* k, const void* v, long long ld, int dtype,
-                                           const float* pre, long long ld_pre, const float* bias, float p0, float q_scale,
+                                           float* pre, long long ld_pre, const float* bias, float p0, float q_scale,
                                            float* state, float* norm_state, float* max_state, const int* cu_tokens,
                                            const int* slots, float* out, long long ld_o, int requests, int n_tokens, int heads,
                                            int dim, int vdim, int write_state, float* workspace, long long workspace_floats,
@@ -417,7 +489,7 @@ HFEE_API int hfee_gated_recurrence_chunked(int mode, const void* q, const void* 
   HFEE_REQUIRE(workspace != nullptr && workspace_floats >= hfee_gated_recurrence_workspace(requests, n_tokens, heads, dim, vdim),
                "gated_recurrence: the workspace is too small");
   RecurrenceArgs p{ld, pre, ld_pre, bias, p0, q_scale, state, norm_state, max_state, cu_tokens, slots, out, ld_o, heads, dim, vdim, write_state,
-                   requests, nullptr, nullptr, nullptr, nullptr, 0};
+                   requests, nullptr, nullptr, nullptr, nullptr, 0, 0};
   p.run_state = workspace;
   p.run_norm = p.run_state + max_runs * heads * dim * vdim;
   p.run_decay = p.run_norm + max_runs * heads * dim;

@@ -1812,7 +1812,8 @@ def gated_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     ``norm_state`` [slots, heads, dim] and ``max_state`` [slots, heads].  ``q`` (times ``q_scale``), ``k``, ``v`` are
     column slices of one buffer; ``state`` [slots, heads, dim, vdim]; ``out`` [n, heads * vdim] float32.  With ``workspace``
     (float32, :func:`gated_recurrence_workspace`) and a request that brings RECURRENCE_CHUNKED_MIN tokens or more, runs of 64
-    tokens are walked side by side (the same recurrence in another association)."""
+    tokens are walked side by side (the same recurrence in another association); with the channel decay that path
+    overwrites ``pre`` with the decays."""
     lib = library()
     ld = _rows(q, "q")
     assert _rows(k, "k") == ld and _rows(v, "v") == ld and q.dtype == k.dtype == v.dtype
