@@ -130,6 +130,87 @@ layernorm_kernel(float* __restrict__ x, const float* __restrict__ residual_add, 
   }
 }
 
+// The same for widths that are multiples of 4 with 16-byte accesses: a thread owns the pieces tid, tid + ROW_THREADS, ...,
+// NCH of them (rows of at most ROW_THREADS * 4 * NCH values), all requested before the first is used and kept in
+// registers between the passes.
+template <typename TOut, int NCH>
+__global__ void __launch_bounds__(ROW_THREADS)
+layernorm_vec_kernel(float* __restrict__ x, const float* __restrict__ residual_add, const float* __restrict__ w,
+                     const int* __restrict__ rows, TOut* __restrict__ out, long long ld_o, int width, float eps) {
+  __shared__ float partial[ROW_THREADS / 32];
+  const int r = blockIdx.x, tid = threadIdx.x;
+  float4 wv[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (tid + j * ROW_THREADS) * 4;
+    wv[j] = c < width ? __ldg(reinterpret_cast<const float4*>(w + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const int src_row = rows ? rows[r] : r;
+  pdl_wait();
+  pdl_launch_dependents();
+  float* xr = x + (long long)src_row * width;
+  const float* ar = residual_add != nullptr ? residual_add + (long long)r * width : nullptr;
+  float4 v[NCH];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (tid + j * ROW_THREADS) * 4;
+    v[j] = c < width ? *reinterpret_cast<const float4*>(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (ar != nullptr) {
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      const int c = (tid + j * ROW_THREADS) * 4;
+      if (c < width) {
+        const float4 a = *reinterpret_cast<const float4*>(ar + c);
+        v[j].x += a.x; v[j].y += a.y; v[j].z += a.z; v[j].w += a.w;
+        *reinterpret_cast<float4*>(xr + c) = v[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+  const float mean = block_total<ROW_THREADS>(sum, partial) / (float)width;
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (tid + j * ROW_THREADS) * 4;
+    if (c < width) {
+      const float a = v[j].x - mean, b = v[j].y - mean, cc = v[j].z - mean, d = v[j].w - mean;
+      ss = fmaf(a, a, ss); ss = fmaf(b, b, ss); ss = fmaf(cc, cc, ss); ss = fmaf(d, d, ss);
+    }
+  }
+  const float scale = 1.0f / sqrtf(block_total<ROW_THREADS>(ss, partial) / (float)width + eps);
+  TOut* orow = out + (long long)r * ld_o;
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    const int c = (tid + j * ROW_THREADS) * 4;
+    if (c >= width) continue;
+    const float o0 = (v[j].x - mean) * scale * wv[j].x, o1 = (v[j].y - mean) * scale * wv[j].y;
+    const float o2 = (v[j].z - mean) * scale * wv[j].z, o3 = (v[j].w - mean) * scale * wv[j].w;
+    if constexpr (sizeof(TOut) == 4) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(orow) + c) = make_float4(o0, o1, o2, o3);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(o0, o1), hi = __floats2bfloat162_rn(o2, o3);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(orow) + c) =
+          make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+  }
+}
+
+__global__ void add_bias_vec_kernel(float4* __restrict__ x, long long ld4, const float4* __restrict__ bias, int cols4, long long total4) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= total4) return;
+  const long long r = e / cols4;
+  const int c = (int)(e - r * cols4);
+  float4 v = x[r * ld4 + c];
+  const float4 b = __ldg(bias + c);
+  v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+  x[r * ld4 + c] = v;
+}
+
 __global__ void add_bias_kernel(float* __restrict__ x, long long ld, const float* __restrict__ bias, int cols, long long total) {
   pdl_wait();
   pdl_launch_dependents();
@@ -143,7 +224,13 @@ __global__ void add_bias_kernel(float* __restrict__ x, long long ld, const float
 template <typename TOut>
 void launch_layernorm(float* x, const float* residual_add, const float* w, const int* rows, void* out, long long ld_o, int n,
                       int width, float eps, cudaStream_t stream) {
-  if (width <= ROW_THREADS * 4)
+  const bool vec = width % 4 == 0 && ld_o % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                   (residual_add == nullptr || (uintptr_t)residual_add % 16 == 0);
+  if (vec && width <= ROW_THREADS * 4 * 2)
+    hfee_launch(layernorm_vec_kernel<TOut, 2>, dim3(n), dim3(ROW_THREADS), 0, stream, x, residual_add, w, rows, (TOut*)out, ld_o, width, eps);
+  else if (vec && width <= ROW_THREADS * 4 * 8)
+    hfee_launch(layernorm_vec_kernel<TOut, 8>, dim3(n), dim3(ROW_THREADS), 0, stream, x, residual_add, w, rows, (TOut*)out, ld_o, width, eps);
+  else if (width <= ROW_THREADS * 4)
     hfee_launch(layernorm_kernel<TOut, 4>, dim3(n), dim3(ROW_THREADS), 0, stream, x, residual_add, w, rows, (TOut*)out, ld_o, width, eps);
   else
     hfee_launch(layernorm_kernel<TOut, 16>, dim3(n), dim3(ROW_THREADS), 0, stream, x, residual_add, w, rows, (TOut*)out, ld_o, width, eps);
@@ -193,6 +280,11 @@ HFEE_API int hfee_add_bias(float* x, long long ld, const float* bias, int rows, 
   if (rows == 0 || cols == 0) return HFEE_OK;
   HFEE_REQUIRE(rows > 0 && cols > 0 && ld >= cols, "add_bias: bad sizes");
   const long long total = (long long)rows * cols;
+  if (cols % 4 == 0 && ld % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)bias % 16 == 0) {
+    hfee_launch(add_bias_vec_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (float4*)x, ld / 4, (const float4*)bias,
+                cols / 4, total / 4);
+    return hfee_check_launch("add_bias");
+  }
   hfee_launch(add_bias_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, ld, bias, cols, total);
   return hfee_check_launch("add_bias");
 }
