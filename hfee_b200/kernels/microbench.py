@@ -402,12 +402,111 @@ def _row_ops(args) -> dict:
     return res
 
 
+def _softmax_attention(args) -> dict:
+    """Windowed softmax attention with a sink (``--window``, 0: none): one prompt portion, or a decode step of ``--batch``."""
+    heads, kv, hd, vd, page = args.heads, args.kv_heads, args.head_dim, args.value_dim or args.head_dim, args.page_size
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([args.context_before], [args.tokens])
+    b = _batch_of(before, new)
+    b.planning_context, b.attention_splits = b.max_context, args.splits or None
+    max_pages = -(-b.max_context // page)
+    table = torch.randperm(b.r * max_pages).reshape(b.r, max_pages).to(torch.int32).to(DEV)
+    kp = torch.randn(b.r * max_pages, kv, page, hd, device=DEV).to(torch.bfloat16)
+    vp = torch.randn(b.r * max_pages, kv, page, vd, device=DEV).to(torch.bfloat16)
+    q = torch.randn(b.n, heads * hd, device=DEV).to(torch.bfloat16)
+    out = torch.empty(b.n, heads * vd, dtype=torch.bfloat16, device=DEV)
+    sink = torch.linspace(-1.0, 2.0, heads, device=DEV)
+    tile = ops.distance_attention_tile(hd, vd)
+    scratch = torch.empty(b.r * heads * ops.MAX_SPLITS * (tile + 2), dtype=torch.float32, device=DEV) if args.decode and tile else None
+    fn = lambda i: ops.softmax_attention(q, kp, vp, table, page, b, out, heads, kv, hd, vd, hd ** -0.5, args.window, sink, 1.0, scratch)
+    sec = _time(fn, args.warmup, args.iters)
+    w = args.window or (1 << 30)
+    seen = lambda s, c: sum(min(w, s + j + 1) for j in range(c))          # keys each new token reads
+    kv_bytes = sum(min(s + c, w + c) for s, c in zip(before, new)) * kv * (hd + vd) * 2
+    flops = sum(2.0 * heads * (hd + vd) * seen(s, c) for s, c in zip(before, new))
+    return {"kernel": "softmax_attention", "heads": heads, "kv_heads": kv, "head_dim": hd, "value_dim": vd, "requests": b.r,
+            "context": b.max_context, "window": args.window, "us": round(sec * 1e6, 2), "kv_gbs": round(kv_bytes / sec / 1e9, 1),
+            "tflops": round(flops / sec / 1e12, 1)}
+
+
+def _gated_recurrence(args, mode: int) -> dict:
+    """The gated matrix-state recurrences (``gla``: a decay per key channel; ``matrix_memory``: exponential gates) of
+    ``--heads`` heads with keys of ``--head-dim`` and values of ``--value-dim``: one prompt portion of ``--tokens`` tokens
+    (walked as runs side by side), or a decode step of ``--batch`` requests."""
+    heads, d, vd = args.heads, args.head_dim, args.value_dim or args.head_dim
+    before, new = ([args.context] * args.batch, [1] * args.batch) if args.decode else ([0], [args.tokens])
+    b = _batch_of(before, new)
+    qk, vc = heads * d, heads * vd
+    proj = (torch.randn(b.n, 2 * qk + vc, device=DEV) * 0.5).to(torch.bfloat16)
+    pre = torch.randn(b.n, qk if mode == 0 else 2 * heads, device=DEV)
+    keep = pre.clone()
+    bias = torch.full((pre.shape[1],), 2.0, device=DEV)
+    S = torch.zeros(b.r, heads, d, vd, device=DEV)
+    N, M = torch.zeros(b.r, heads, d, device=DEV), torch.zeros(b.r, heads, device=DEV)
+    out = torch.empty(b.n, vc, device=DEV)
+    ws = torch.empty(ops.gated_recurrence_workspace(b.r, b.n, heads, d, vd), device=DEV)
+
+    def fn(i):
+        if mode == 0 and b.max_new >= ops.RECURRENCE_CHUNKED_MIN:
+            pre.copy_(keep)                # the chunked path turns the gates into decays in place
+        ops.gated_recurrence(mode, proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:], pre, bias, 1.0 / 16 if mode == 0 else 15.0,
+                             d ** -0.5, S, b, out, heads, d, vd, True, N if mode else None, M if mode else None, ws)
+    sec = _time(fn, args.warmup, args.iters)
+    chunked = b.max_new >= ops.RECURRENCE_CHUNKED_MIN
+    flops = (2 if chunked else 1) * b.n * heads * d * vd * (5.0 if mode == 0 else 5.0)      # a chunked walk visits a token twice
+    io = b.n * ((2 * qk + vc) * 2 + pre.shape[1] * 4 + vc * 4) + 2 * b.r * heads * d * vd * 4
+    return {"kernel": "gla" if mode == 0 else "matrix_memory", "heads": heads, "key_dim": d, "value_dim": vd, "tokens": b.n,
+            "requests": b.r, "chunked": chunked, "us": round(sec * 1e6, 2), "fp32_tflops": round(flops / sec / 1e12, 2),
+            "io_gbs": round(io / sec / 1e9, 1)}
+
+
+def _pupinex_rows(args) -> dict:
+    """Row kernels of the Pupinex parts on ``--tokens`` rows of width ``--k``: layer norm, the bigram embedding, the bias,
+    the step between the q/k/v projection and the attention, and the per-head norm with its gate."""
+    n, w = args.tokens, args.k
+    res = {"kernel": "pupinex_rows", "tokens": n, "width": w}
+    x, nw = torch.randn(n, w, device=DEV), torch.ones(w, device=DEV)
+    out = torch.empty(n, w, dtype=torch.bfloat16, device=DEV)
+    sec = _time(lambda i: ops.layernorm(x, nw, out, 1e-5), args.warmup, args.iters)
+    res["layernorm"] = {"us": round(sec * 1e6, 2), "gbs": round(n * w * 6 / sec / 1e9, 1)}
+    sec = _time(lambda i: ops.rmsnorm(x, nw, out, 1e-5), args.warmup, args.iters)
+    res["rmsnorm"] = {"us": round(sec * 1e6, 2), "gbs": round(n * w * 6 / sec / 1e9, 1)}
+    sec = _time(lambda i: ops.add_bias(x, nw), args.warmup, args.iters)
+    res["add_bias"] = {"us": round(sec * 1e6, 2), "gbs": round(n * w * 8 / sec / 1e9, 1)}
+    b = _batch_of([0], [n])
+    b.token_ids = torch.randint(0, 32768, (n,), dtype=torch.int32, device=DEV)
+    b.feedback = None
+    table = torch.randn(32768, w, device=DEV).to(torch.bfloat16)
+    pairs = torch.randn(65522, w, device=DEV).to(torch.bfloat16)
+    last = torch.zeros(b.r, 1, dtype=torch.int32, device=DEV)
+    sec = _time(lambda i: ops.embed_bigram(table, pairs, b, last, x, 65521, 1000003, 31), args.warmup, args.iters)
+    res["embed_bigram"] = {"us": round(sec * 1e6, 2), "gbs": round(n * w * 8 / sec / 1e9, 1)}
+    heads, kv, hd, page = args.heads, args.kv_heads, args.head_dim, args.page_size
+    cols = (heads + 2 * kv) * hd
+    proj = torch.randn(n, cols, device=DEV).to(torch.bfloat16)
+    max_pages = -(-n // page)
+    tbl = torch.arange(max_pages, dtype=torch.int32, device=DEV).reshape(1, max_pages)
+    kp = torch.zeros(max_pages, kv, page, hd, dtype=torch.bfloat16, device=DEV)
+    vp = torch.zeros_like(kp)
+    q = torch.empty(n, heads * hd, dtype=torch.bfloat16, device=DEV)
+    cs = torch.rand(n, hd // 4, 2, device=DEV)
+    bias = [torch.zeros(c, device=DEV) for c in (heads * hd, kv * hd, kv * hd)]
+    norms = (torch.ones(heads * hd, device=DEV), torch.ones(kv * hd, device=DEV))
+    sec = _time(lambda i: ops.attention_prepare(proj, 0, heads * hd, (heads + kv) * hd, heads, kv, hd, hd, b, q, kp, vp, tbl, page, cs,
+                                                hd // 2, False, tuple(bias), norms, 1e-5), args.warmup, args.iters)
+    res["attention_prepare"] = {"us": round(sec * 1e6, 2), "gbs": round(n * cols * 4 / sec / 1e9, 1)}
+    o, g = torch.randn(n, w, device=DEV), torch.randn(n, w, device=DEV).to(torch.bfloat16)
+    sec = _time(lambda i: ops.head_norm_gate_scaled(o, nw, 1e-5, g, out, 8, w // 8, "sigmoid", 0.5), args.warmup, args.iters)
+    res["head_norm_gate"] = {"us": round(sec * 1e6, 2), "gbs": round(n * w * 8 / sec / 1e9, 1)}
+    return res
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("kernel", choices=["delta_rule", "conv_act", "latent_attention", "head_linear", "rope_norm_cache",
                                        "gemm_tcgen05", "gemm_stream", "gemm_skinny", "gemm_ring", "gemm_pair", "attention_decode", "attention_prefill",
                                       "sigmoid_attention", "linear_attention", "mingru", "selective_scan",
-                                       "distance_attention", "moe_experts", "row_ops"])
+                                       "distance_attention", "moe_experts", "row_ops", "softmax_attention", "gla", "matrix_memory",
+                                       "pupinex_rows"])
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -457,6 +556,12 @@ def main(argv=None) -> int:
     elif args.kernel in ("mingru", "selective_scan", "distance_attention", "moe_experts", "row_ops"):
         res = {"mingru": _mingru, "selective_scan": _selective_scan, "distance_attention": _distance_attention,
                "moe_experts": _moe_experts, "row_ops": _row_ops}[args.kernel](args)
+    elif args.kernel == "softmax_attention":
+        res = _softmax_attention(args)
+    elif args.kernel in ("gla", "matrix_memory"):
+        res = _gated_recurrence(args, 0 if args.kernel == "gla" else 1)
+    elif args.kernel == "pupinex_rows":
+        res = _pupinex_rows(args)
     else:
         res = _attention(args, args.kernel == "attention_decode")
     print(json.dumps(res))
