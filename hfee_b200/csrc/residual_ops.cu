@@ -55,6 +55,8 @@ __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, 
   return g / (1.f + expf(-alpha * g)) * (u + shift);
 }
 
+constexpr int GLU_SPAN = 4 * ROW_THREADS;
+
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
 clamped_glu_kernel(const T* __restrict__ gate_up, long long ld_in, T* __restrict__ out, long long ld_out, int inner,
@@ -63,7 +65,9 @@ clamped_glu_kernel(const T* __restrict__ gate_up, long long ld_in, T* __restrict
   pdl_launch_dependents();
   const T* in = gate_up + (long long)blockIdx.x * ld_in;
   T* o = out + (long long)blockIdx.x * ld_out;
-  for (int c = threadIdx.x; c < inner; c += ROW_THREADS) {
+  // a block owns a span of GLU_SPAN columns of its row, so that a few rows (a decode step) still fill the SMs
+  const int end = min(inner, (int)(blockIdx.y + 1) * GLU_SPAN);
+  for (int c = blockIdx.y * GLU_SPAN + threadIdx.x; c < end; c += ROW_THREADS) {
     const int at = (c / granule) * 2 * granule + c % granule;
     o[c] = from_f32<T>(clamped_glu(to_f32<T>(in[at]), to_f32<T>(in[at + granule]), limit, alpha, shift));
   }
@@ -144,10 +148,10 @@ HFEE_API int hfee_clamped_glu(const void* gate_up, long long ld_in, void* out, l
   HFEE_REQUIRE(n > 0 && inner > 0 && granule > 0 && inner % granule == 0, "clamped_glu: inner %d is not a multiple of the granule %d", inner, granule);
   HFEE_REQUIRE(ld_in >= 2 * inner && ld_out >= inner && limit > 0.f, "clamped_glu: a row stride is too small or the limit is not positive");
   if (dtype == HFEE_F32)
-    hfee_launch(clamped_glu_kernel<float>, dim3(n), dim3(ROW_THREADS), 0, stream, (const float*)gate_up, ld_in, (float*)out, ld_out,
+    hfee_launch(clamped_glu_kernel<float>, dim3(n, (inner + GLU_SPAN - 1) / GLU_SPAN), dim3(ROW_THREADS), 0, stream, (const float*)gate_up, ld_in, (float*)out, ld_out,
                 inner, granule, limit, alpha, shift);
   else if (dtype == HFEE_BF16)
-    hfee_launch(clamped_glu_kernel<__nv_bfloat16>, dim3(n), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)gate_up, ld_in,
+    hfee_launch(clamped_glu_kernel<__nv_bfloat16>, dim3(n, (inner + GLU_SPAN - 1) / GLU_SPAN), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)gate_up, ld_in,
                 (__nv_bfloat16*)out, ld_out, inner, granule, limit, alpha, shift);
   else
     return hfee_fail(HFEE_ERR_ARG, "clamped_glu: unknown dtype %d", dtype);
